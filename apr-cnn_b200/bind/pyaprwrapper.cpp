@@ -1,0 +1,514 @@
+// Python module `_pyaprwrapper`: the host side of the drop-in boundary.
+//
+// Mirrors the part of the reference's extension module that the particle-domain CNN path uses
+// (wrappers/pythonBind.cpp:63-184): `data_containers.APR` / `APRPtrVector`
+// (pyapr/data_containers/src/BindAPR.hpp:44-133), `aprnet.utils.number_*`
+// (pyapr/aprnet/src/utils.hpp:340-382) and the `aprnet.cuda.*` operator functions
+// (wrappers/pythonBind.cpp:162-181) with the same names, keyword names, tensor conventions and error
+// behaviour (pyapr/aprnet/cuda/src/wrap_*_gpu.hpp).  This layer owns tensor allocation, the batch
+// loop and error -> exception translation; all arithmetic happens in libaprnet_b200 behind the C ABI
+// declared in include/aprnet_b200.h.  There is no CPU implementation: a non-CUDA tensor is an error.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+#include <pybind11/stl_bind.h>
+#include <pybind11/numpy.h>
+
+#include <cmath>
+#include <cstdint>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/aprnet_b200.h"
+
+namespace py = pybind11;
+
+#define CHECK_CUDA(x) TORCH_CHECK(x.device().is_cuda(), #x " must be a CUDA tensor")
+#define CHECK_CONTIGUOUS(x) TORCH_CHECK(x.is_contiguous(), #x " must be contiguous")
+#define CHECK_INPUT(x) CHECK_CUDA(x); CHECK_CONTIGUOUS(x)
+
+// ---------------------------------------------------------------------------------------------
+// APR: host copy of the linear access arrays + the device handle created by init_cuda()
+// ---------------------------------------------------------------------------------------------
+class APR {
+public:
+    std::string name;
+    int org_dims_[3] = {0, 0, 0};            // (y, x, z) as in the reference's APR::org_dims
+    int level_min_ = 0, level_max_ = 0;
+    std::vector<int> dims_zxy;               // 3 * (level_max + 1)
+    std::vector<int64_t> row_ptr, tree_row_ptr;
+    std::vector<uint16_t> y_vec, tree_y_vec;
+    std::vector<int64_t> row_off, trow_off;  // first row of each level
+    aprnet_apr* dev = nullptr;
+    int dev_index = -1;
+    bool initialized = false;
+
+    APR() = default;
+    APR(const APR&) = delete;
+    APR& operator=(const APR&) = delete;
+    ~APR() { if (dev) aprnet_apr_destroy(dev); }
+
+    void init(int z, int x, int y, py::array_t<int64_t, py::array::c_style | py::array::forcecast> rp,
+              py::array_t<uint16_t, py::array::c_style | py::array::forcecast> yv,
+              py::array_t<int64_t, py::array::c_style | py::array::forcecast> trp,
+              py::array_t<uint16_t, py::array::c_style | py::array::forcecast> tyv) {
+        org_dims_[0] = y; org_dims_[1] = x; org_dims_[2] = z;
+        const int mx = std::max(z, std::max(x, y));
+        level_max_ = std::max(1, (int) std::ceil(std::log2((double) mx)));
+        level_min_ = 1;
+        dims_zxy.resize(3 * (level_max_ + 1));
+        for (int l = 0; l <= level_max_; ++l) {
+            const double s = std::pow(2.0, level_max_ - l);
+            dims_zxy[3 * l] = (int) std::ceil(z / s);
+            dims_zxy[3 * l + 1] = (int) std::ceil(x / s);
+            dims_zxy[3 * l + 2] = (int) std::ceil(y / s);
+        }
+        row_off.assign(level_max_ + 2, 0);
+        trow_off.assign(level_max_ + 2, 0);
+        for (int l = 0; l <= level_max_; ++l) {
+            const int64_t rows = (int64_t) dims_zxy[3 * l] * dims_zxy[3 * l + 1];
+            row_off[l + 1] = row_off[l] + (l >= level_min_ ? rows : 0);
+            trow_off[l + 1] = trow_off[l] + (l <= level_max_ - 1 ? rows : 0);
+        }
+        if (rp.size() != row_off[level_max_ + 1] + 1) throw std::invalid_argument("APR: row_ptr has the wrong length");
+        if (trp.size() != trow_off[level_max_] + 1) throw std::invalid_argument("APR: tree_row_ptr has the wrong length");
+        row_ptr.assign(rp.data(), rp.data() + rp.size());
+        tree_row_ptr.assign(trp.data(), trp.data() + trp.size());
+        if (yv.size() != row_ptr.back() || tyv.size() != tree_row_ptr.back())
+            throw std::invalid_argument("APR: y arrays do not match the row pointers");
+        y_vec.assign(yv.data(), yv.data() + yv.size());
+        tree_y_vec.assign(tyv.data(), tyv.data() + tyv.size());
+        if (dev) { aprnet_apr_destroy(dev); dev = nullptr; }
+        initialized = true;
+    }
+
+    int level_min() const { return level_min_; }
+    int level_max() const { return level_max_; }
+    int z_num(int l) const { return dims_zxy.at(3 * l); }
+    int x_num(int l) const { return dims_zxy.at(3 * l + 1); }
+    int y_num(int l) const { return dims_zxy.at(3 * l + 2); }
+    int org_dims(int d) const { return org_dims_[d]; }
+    uint64_t total_number_particles() const { return y_vec.size(); }
+    uint64_t total_number_tree_particles() const { return tree_y_vec.size(); }
+    double computational_ratio() const {
+        return (double) org_dims_[0] * org_dims_[1] * org_dims_[2] / (double) std::max<size_t>(y_vec.size(), 1);
+    }
+
+    int64_t particles_level_end(int l) const { return row_ptr[row_off[l + 1]]; }
+    int64_t tree_level_begin(int l) const { return tree_row_ptr[trow_off[l]]; }
+    int64_t tree_level_end(int l) const { return tree_row_ptr[trow_off[l + 1]]; }
+
+    // pyapr/aprnet/src/helpers.hpp:86-101
+    int64_t number_parts(int level_delta) const {
+        const int cml = level_max_ - level_delta;
+        if (cml < 0 || cml > level_max_) throw std::invalid_argument("level_delta out of range");
+        int64_t n = particles_level_end(cml);
+        if (cml <= level_max_ - 1) n += tree_level_end(cml) - tree_level_begin(cml);
+        return n;
+    }
+
+    // copy access structures to the current CUDA device (the reference's APR::init_cuda)
+    void init_cuda(bool with_tree) {
+        (void) with_tree;
+        if (!initialized) throw std::runtime_error("APR is not initialized");
+        const int device = (int) c10::cuda::current_device();
+        if (dev && dev_index == device) return;
+        if (dev) { aprnet_apr_destroy(dev); dev = nullptr; }
+        const int rc = aprnet_apr_create(&dev, level_min_, level_max_, dims_zxy.data(), row_ptr.data(), y_vec.data(),
+                                         tree_row_ptr.data(), tree_y_vec.data(), device);
+        if (rc != APRNET_OK) throw std::runtime_error(std::string("APR.init_cuda failed: ") + aprnet_last_error());
+        dev_index = device;
+    }
+
+    aprnet_apr* handle(const torch::Tensor& like) const {
+        TORCH_CHECK(dev != nullptr, "APR.init_cuda() must be called before using the CUDA operators");
+        TORCH_CHECK(like.device().index() == dev_index, "APR access data lives on cuda:", dev_index, " but the tensor is on ", like.device());
+        return dev;
+    }
+};
+
+PYBIND11_MAKE_OPAQUE(std::vector<APR*>)
+
+namespace {
+
+inline void check(int rc, const char* what) {
+    TORCH_CHECK(rc == APRNET_OK, what, " failed (", rc, "): ", aprnet_last_error());
+}
+
+inline int dtype_id(const torch::Tensor& t) {
+    if (t.scalar_type() == torch::kFloat32) return APRNET_F32;
+    if (t.scalar_type() == torch::kFloat64) return APRNET_F64;
+    TORCH_CHECK(false, "aprnet CUDA operators support float32 and float64 tensors, got ", t.scalar_type());
+    return -1;
+}
+
+inline void* stream_of(const torch::Tensor& t) { return (void*) at::cuda::getCurrentCUDAStream(t.device().index()).stream(); }
+
+inline std::vector<int> read_level_delta(const torch::Tensor& level_delta, size_t batch) {
+    TORCH_CHECK(!level_delta.device().is_cuda(), "level_delta must be a CPU tensor");
+    TORCH_CHECK(level_delta.scalar_type() == torch::kInt32 && level_delta.dim() == 1, "level_delta must be a 1-D int32 tensor");
+    TORCH_CHECK((size_t) level_delta.size(0) >= batch, "level_delta has fewer entries than the batch");
+    auto acc = level_delta.accessor<int, 1>();
+    std::vector<int> out(batch);
+    for (size_t i = 0; i < batch; ++i) out[i] = acc[i];
+    return out;
+}
+
+inline void check_batch(const std::vector<APR*>& aprs, const torch::Tensor& t) {
+    TORCH_CHECK(t.dim() == 3, "expected a (batch, channels, particles) tensor");
+    TORCH_CHECK((int64_t) aprs.size() == t.size(0), "number of APRs (", aprs.size(), ") does not match the batch size (", t.size(0), ")");
+}
+
+// pyapr/aprnet/cuda/src/common.hpp:17 (CHECK_LEVEL_DELTA against tree level_max + 1 = level_max)
+inline void check_level_delta(const APR& apr, int dl) {
+    TORCH_CHECK(dl >= 0 && apr.level_max() > dl, "level delta ", dl, " is too large for APR with maximum level ", apr.level_max());
+}
+
+inline size_t esize(const torch::Tensor& t) { return t.element_size(); }
+inline char* row(const torch::Tensor& t, int64_t b) { return (char*) t.data_ptr() + b * t.stride(0) * (int64_t) esize(t); }
+
+// zero the padding behind the valid entries of batch item b
+inline void zero_padding(torch::Tensor& t, int64_t b, int64_t valid) {
+    if (valid < t.size(2)) t.select(0, b).narrow(1, valid, t.size(2) - valid).zero_();
+}
+
+// ---- 3x3x3 convolution ------------------------------------------------------------------------
+torch::Tensor conv333_forward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights, torch::Tensor level_delta) {
+    CHECK_INPUT(input); CHECK_INPUT(weights);
+    check_batch(aprs, input);
+    TORCH_CHECK(weights.dim() == 6 && weights.size(3) == 3 && weights.size(4) == 3 && weights.size(5) == 3, "weights must be (levels, Cout, Cin, 3, 3, 3)");
+    TORCH_CHECK(input.size(1) == weights.size(2), "input tensor shape does not match weights tensor");
+    TORCH_CHECK(input.scalar_type() == weights.scalar_type(), "input and weights must have the same dtype");
+    c10::cuda::CUDAGuard guard(input.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    int64_t max_tree = 1;
+    for (size_t i = 0; i < aprs.size(); ++i) {
+        check_level_delta(*aprs[i], dl[i]);
+        max_tree = std::max<int64_t>(max_tree, aprnet_tree_size(aprs[i]->handle(input), dl[i]));
+        TORCH_CHECK(aprs[i]->number_parts(dl[i]) <= input.size(2), "input has fewer particles than the APR at this level delta");
+    }
+    const int64_t cin = input.size(1), cout = weights.size(1), n = input.size(2);
+    auto output = torch::empty({input.size(0), cout, n}, input.options());
+    auto tree = torch::empty({cin, max_tree}, input.options());
+    const int dt = dtype_id(input);
+    for (int64_t b = 0; b < input.size(0); ++b) {
+        check(aprnet_conv333_forward(aprs[b]->handle(input), dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(input, b), n,
+                                     weights.data_ptr(), row(output, b), n, tree.data_ptr(), max_tree, stream_of(input)),
+              "conv333_forward");
+        zero_padding(output, b, aprs[b]->number_parts(dl[b]));
+    }
+    return output;
+}
+
+std::vector<torch::Tensor> conv333_backward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights,
+                                            torch::Tensor grad_output, torch::Tensor level_delta) {
+    CHECK_INPUT(input); CHECK_INPUT(weights); CHECK_INPUT(grad_output);
+    check_batch(aprs, input);
+    TORCH_CHECK(grad_output.dim() == 3 && grad_output.size(0) == input.size(0) && grad_output.size(1) == weights.size(1) &&
+                grad_output.size(2) == input.size(2), "grad_output shape does not match");
+    TORCH_CHECK(input.size(1) == weights.size(2), "input tensor shape does not match weights tensor");
+    c10::cuda::CUDAGuard guard(input.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    int64_t max_tree = 1;
+    for (size_t i = 0; i < aprs.size(); ++i) {
+        check_level_delta(*aprs[i], dl[i]);
+        max_tree = std::max<int64_t>(max_tree, aprnet_tree_size(aprs[i]->handle(input), dl[i]));
+    }
+    const int64_t cin = input.size(1), cout = weights.size(1), n = input.size(2);
+    auto tree = torch::empty({cin, max_tree}, input.options());
+    auto grad_tree = torch::empty({cin, max_tree}, input.options());
+    auto grad_input = torch::zeros_like(input);
+    auto grad_weights = torch::zeros_like(weights);
+    auto partial = torch::empty({aprnet_conv333_partial_elems((int) cin, (int) cout)}, input.options());
+    const int dt = dtype_id(input);
+    void* st = stream_of(input);
+    for (int64_t b = 0; b < input.size(0); ++b) {
+        aprnet_apr* h = aprs[b]->handle(input);
+        check(aprnet_fill_tree_mean_forward(h, dl[b], dt, (int) cin, row(input, b), n, tree.data_ptr(), max_tree, st), "fill_tree_mean");
+        check(aprnet_conv333_backward_weights(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(input, b), n,
+                                              tree.data_ptr(), max_tree, row(grad_output, b), n, grad_weights.data_ptr(),
+                                              partial.data_ptr(), st), "conv333_backward_weights");
+        check(aprnet_conv333_backward_input(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(grad_output, b), n,
+                                            weights.data_ptr(), row(grad_input, b), n, grad_tree.data_ptr(), max_tree, st),
+              "conv333_backward_input");
+    }
+    return {grad_input, grad_weights};
+}
+
+// ---- 1x1x1 convolution ------------------------------------------------------------------------
+torch::Tensor conv111_forward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights, torch::Tensor level_delta) {
+    CHECK_INPUT(input); CHECK_INPUT(weights);
+    check_batch(aprs, input);
+    TORCH_CHECK(weights.dim() == 6 && weights.size(3) == 1 && weights.size(4) == 1 && weights.size(5) == 1, "weights must be (stencils, Cout, Cin, 1, 1, 1)");
+    TORCH_CHECK(input.size(1) == weights.size(2), "input tensor shape does not match weights tensor");
+    c10::cuda::CUDAGuard guard(input.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    const int64_t cin = input.size(1), cout = weights.size(1), n = input.size(2);
+    auto output = torch::empty({input.size(0), cout, n}, input.options());
+    const int dt = dtype_id(input);
+    for (int64_t b = 0; b < input.size(0); ++b) {
+        check_level_delta(*aprs[b], dl[b]);
+        check(aprnet_conv111_forward(aprs[b]->handle(input), dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(input, b), n,
+                                     weights.data_ptr(), row(output, b), n, stream_of(input)), "conv111_forward");
+        zero_padding(output, b, aprs[b]->number_parts(dl[b]));
+    }
+    return output;
+}
+
+std::vector<torch::Tensor> conv111_backward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights,
+                                            torch::Tensor grad_output, torch::Tensor level_delta) {
+    CHECK_INPUT(input); CHECK_INPUT(weights); CHECK_INPUT(grad_output);
+    check_batch(aprs, input);
+    TORCH_CHECK(grad_output.dim() == 3 && grad_output.size(1) == weights.size(1) && grad_output.size(2) == input.size(2), "grad_output shape does not match");
+    c10::cuda::CUDAGuard guard(input.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    const int64_t cin = input.size(1), cout = weights.size(1), n = input.size(2);
+    auto grad_input = torch::empty_like(input);
+    auto grad_weights = torch::zeros_like(weights);
+    auto partial = torch::empty({aprnet_conv111_partial_elems((int) cin, (int) cout)}, input.options());
+    const int dt = dtype_id(input);
+    void* st = stream_of(input);
+    for (int64_t b = 0; b < input.size(0); ++b) {
+        check_level_delta(*aprs[b], dl[b]);
+        aprnet_apr* h = aprs[b]->handle(input);
+        check(aprnet_conv111_backward_input(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(grad_output, b), n,
+                                            weights.data_ptr(), row(grad_input, b), n, st), "conv111_backward_input");
+        zero_padding(grad_input, b, aprs[b]->number_parts(dl[b]));
+        check(aprnet_conv111_backward_weights(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(input, b), n,
+                                              row(grad_output, b), n, grad_weights.data_ptr(), partial.data_ptr(), st),
+              "conv111_backward_weights");
+    }
+    return {grad_input, grad_weights};
+}
+
+// ---- restriction --------------------------------------------------------------------------------
+torch::Tensor restrict_kernel_333_forward(torch::Tensor weights, const int num_levels) {
+    CHECK_INPUT(weights);
+    TORCH_CHECK(weights.dim() == 6, "weights must be 6-dimensional");
+    TORCH_CHECK(num_levels >= weights.size(0), "restrict_kernel_333_forward requires num_levels >= weights.shape[0]");
+    c10::cuda::CUDAGuard guard(weights.device());
+    auto output = torch::empty({num_levels, weights.size(1), weights.size(2), 3, 3, 3}, weights.options());
+    check(aprnet_restrict333_forward(dtype_id(weights), (int) weights.size(0), num_levels, weights.size(1) * weights.size(2),
+                                     weights.data_ptr(), output.data_ptr(), stream_of(weights)), "restrict_kernel333_forward");
+    return output;
+}
+
+torch::Tensor restrict_kernel_333_backward(torch::Tensor grad_weights_expanded, const int num_levels) {
+    CHECK_INPUT(grad_weights_expanded);
+    TORCH_CHECK(num_levels <= grad_weights_expanded.size(0), "restrict_kernel_333_backward requires num_levels <= grad_weights_expanded.shape[0]");
+    c10::cuda::CUDAGuard guard(grad_weights_expanded.device());
+    auto g = grad_weights_expanded;
+    auto output = torch::empty({num_levels, g.size(1), g.size(2), 3, 3, 3}, g.options());
+    check(aprnet_restrict333_backward(dtype_id(g), num_levels, (int) g.size(0), g.size(1) * g.size(2), g.data_ptr(), output.data_ptr(),
+                                      stream_of(g)), "restrict_kernel333_backward");
+    return output;
+}
+
+// ---- max pooling --------------------------------------------------------------------------------
+std::vector<torch::Tensor> maxpool_forward_cuda(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor level_delta) {
+    CHECK_INPUT(input);
+    check_batch(aprs, input);
+    c10::cuda::CUDAGuard guard(input.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    int64_t max_size = 0;
+    for (size_t i = 0; i < aprs.size(); ++i) {
+        TORCH_CHECK(dl[i] >= 0 && aprs[i]->level_max() - dl[i] - 1 >= aprs[i]->level_min(), "level delta ", dl[i], " is too large to pool this APR");
+        max_size = std::max(max_size, aprs[i]->number_parts(dl[i] + 1));
+    }
+    auto output = torch::empty({input.size(0), input.size(1), max_size}, input.options());
+    auto max_indices = torch::zeros({input.size(0), input.size(1), max_size}, input.options().dtype(torch::kLong));
+    const int dt = dtype_id(input);
+    for (int64_t b = 0; b < input.size(0); ++b) {
+        check(aprnet_maxpool_forward(aprs[b]->handle(input), dl[b], dt, (int) input.size(1), row(input, b), input.size(2), row(output, b),
+                                     (int64_t*) row(max_indices, b), max_size, stream_of(input)), "maxpool_forward");
+        zero_padding(output, b, aprs[b]->number_parts(dl[b] + 1));
+    }
+    return {output, max_indices};
+}
+
+torch::Tensor maxpool_backward_cuda(std::vector<APR*>& aprs, torch::Tensor grad_output, torch::Tensor max_indices, torch::Tensor level_delta) {
+    CHECK_INPUT(grad_output); CHECK_INPUT(max_indices);
+    check_batch(aprs, grad_output);
+    TORCH_CHECK(max_indices.scalar_type() == torch::kLong && max_indices.sizes() == grad_output.sizes(), "max_indices must be int64 with the shape of grad_output");
+    c10::cuda::CUDAGuard guard(grad_output.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    int64_t max_size = 0;
+    for (size_t i = 0; i < aprs.size(); ++i) max_size = std::max(max_size, aprs[i]->number_parts(dl[i]));
+    auto grad_input = torch::zeros({grad_output.size(0), grad_output.size(1), max_size}, grad_output.options());
+    const int dt = dtype_id(grad_output);
+    for (int64_t b = 0; b < grad_output.size(0); ++b)
+        check(aprnet_maxpool_backward(aprs[b]->handle(grad_output), dl[b], dt, (int) grad_output.size(1), row(grad_output, b),
+                                      (const int64_t*) row(max_indices, b), grad_output.size(2), row(grad_input, b), max_size,
+                                      stream_of(grad_output)), "maxpool_backward");
+    return grad_input;
+}
+
+// ---- up-sampling --------------------------------------------------------------------------------
+torch::Tensor upsample_const_forward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor level_delta) {
+    CHECK_INPUT(input);
+    check_batch(aprs, input);
+    TORCH_CHECK(level_delta.min().item<int>() > 0, "upsample_const_forward assumes all inputs to have level_delta > 0");
+    c10::cuda::CUDAGuard guard(input.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    int64_t max_size = 0;
+    for (size_t i = 0; i < aprs.size(); ++i) max_size = std::max(max_size, aprs[i]->number_parts(dl[i] - 1));
+    auto output = torch::empty({input.size(0), input.size(1), max_size}, input.options());
+    const int dt = dtype_id(input);
+    for (int64_t b = 0; b < input.size(0); ++b) {
+        check(aprnet_upsample_forward(aprs[b]->handle(input), dl[b], dt, (int) input.size(1), row(input, b), input.size(2), row(output, b),
+                                      max_size, stream_of(input)), "upsample_const_forward");
+        zero_padding(output, b, aprs[b]->number_parts(dl[b] - 1));
+    }
+    return output;
+}
+
+torch::Tensor upsample_const_backward(std::vector<APR*>& aprs, torch::Tensor grad_output, torch::Tensor level_delta) {
+    CHECK_INPUT(grad_output);
+    check_batch(aprs, grad_output);
+    TORCH_CHECK(level_delta.min().item<int>() > 0, "upsample_const_backward assumes all inputs to have level_delta > 0");
+    c10::cuda::CUDAGuard guard(grad_output.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    int64_t max_size = 0;
+    for (size_t i = 0; i < aprs.size(); ++i) max_size = std::max(max_size, aprs[i]->number_parts(dl[i]));
+    auto grad_input = torch::empty({grad_output.size(0), grad_output.size(1), max_size}, grad_output.options());
+    const int dt = dtype_id(grad_output);
+    for (int64_t b = 0; b < grad_output.size(0); ++b) {
+        check(aprnet_upsample_backward(aprs[b]->handle(grad_output), dl[b], dt, (int) grad_output.size(1), row(grad_output, b),
+                                       grad_output.size(2), row(grad_input, b), max_size, stream_of(grad_output)), "upsample_const_backward");
+        zero_padding(grad_input, b, aprs[b]->number_parts(dl[b]));
+    }
+    return grad_input;
+}
+
+// ---- tree fill on (C, N) tensors -------------------------------------------------------------------
+torch::Tensor fill_tree(APR& apr, torch::Tensor input, bool use_max) {
+    CHECK_INPUT(input);
+    TORCH_CHECK(input.dim() == 2 && input.size(1) >= (int64_t) apr.total_number_particles(), "expected a (channels, particles) tensor");
+    c10::cuda::CUDAGuard guard(input.device());
+    const int64_t t = std::max<int64_t>(1, (int64_t) apr.total_number_tree_particles());
+    auto tree = torch::empty({input.size(0), t}, input.options());
+    if (use_max)
+        check(aprnet_fill_tree_max(apr.handle(input), dtype_id(input), (int) input.size(0), input.data_ptr(), input.size(1), tree.data_ptr(), t, stream_of(input)), "fill_tree_max");
+    else
+        check(aprnet_fill_tree_mean_full(apr.handle(input), dtype_id(input), (int) input.size(0), input.data_ptr(), input.size(1), tree.data_ptr(), t, stream_of(input)), "fill_tree_mean");
+    return tree.narrow(1, 0, (int64_t) apr.total_number_tree_particles());
+}
+
+torch::Tensor fill_tree_mean_dl(APR& apr, torch::Tensor input, int level_delta) {
+    CHECK_INPUT(input);
+    check_level_delta(apr, level_delta);
+    c10::cuda::CUDAGuard guard(input.device());
+    const int64_t ts = aprnet_tree_size(apr.handle(input), level_delta);
+    auto tree = torch::empty({input.size(0), std::max<int64_t>(ts, 1)}, input.options());
+    check(aprnet_fill_tree_mean_forward(apr.handle(input), level_delta, dtype_id(input), (int) input.size(0), input.data_ptr(), input.size(1),
+                                        tree.data_ptr(), std::max<int64_t>(ts, 1), stream_of(input)), "fill_tree_mean");
+    return tree.narrow(1, 0, ts);
+}
+
+torch::Tensor fill_tree_mean_dl_backward(APR& apr, torch::Tensor grad_input, torch::Tensor grad_tree, int level_delta) {
+    CHECK_INPUT(grad_input); CHECK_INPUT(grad_tree);
+    check_level_delta(apr, level_delta);
+    c10::cuda::CUDAGuard guard(grad_input.device());
+    auto gi = grad_input.clone();
+    auto gt = grad_tree.clone();
+    check(aprnet_fill_tree_mean_backward(apr.handle(gi), level_delta, dtype_id(gi), (int) gi.size(0), gi.data_ptr(), gi.size(1), gt.data_ptr(),
+                                         gt.size(1), stream_of(gi)), "fill_tree_mean_backward");
+    return gi;
+}
+
+py::array_t<int32_t> plan_nbr_table(APR& apr, int level_delta) {
+    TORCH_CHECK(apr.dev != nullptr, "APR.init_cuda() must be called first");
+    py::array_t<int32_t> out({(py::ssize_t) 27, (py::ssize_t) apr.number_parts(level_delta)});
+    check(aprnet_plan_copy_nbr_table(apr.dev, level_delta, out.mutable_data()), "plan_nbr_table");
+    return out;
+}
+
+py::array_t<int32_t> child_table(APR& apr) {
+    TORCH_CHECK(apr.dev != nullptr, "APR.init_cuda() must be called first");
+    py::array_t<int32_t> out({(py::ssize_t) 8, (py::ssize_t) apr.total_number_tree_particles()});
+    check(aprnet_copy_child_table(apr.dev, out.mutable_data()), "child_table");
+    return out;
+}
+
+template<typename T>
+py::array_t<T> to_array(const std::vector<T>& v) { return py::array_t<T>((py::ssize_t) v.size(), v.data()); }
+
+} // namespace
+
+PYBIND11_MODULE(_pyaprwrapper, m) {
+    using namespace pybind11::literals;
+    m.doc() = "B200-native particle-domain CNN operators behind the pyapr extension-module interface";
+    m.attr("__version__") = py::str("aprnet-b200-0.1");
+    m.attr("__cuda_build__") = true;
+
+    py::module data_containers = m.def_submodule("data_containers");
+    py::class_<APR>(data_containers, "APR")
+        .def(py::init())
+        .def("__repr__", [](APR& a) {
+            return "APR(shape [" + std::to_string(a.org_dims(2)) + ", " + std::to_string(a.org_dims(1)) + ", " +
+                   std::to_string(a.org_dims(0)) + "], " + std::to_string(a.total_number_particles()) + " particles)"; })
+        .def_readwrite("name", &APR::name)
+        .def("init_from_arrays", &APR::init, "shape_z"_a, "shape_x"_a, "shape_y"_a, "row_ptr"_a, "y"_a, "tree_row_ptr"_a, "tree_y"_a,
+             "Set the linear access arrays (CSR row pointers and y coordinates of particles and tree nodes)")
+        .def("total_number_particles", &APR::total_number_particles, "return number of particles")
+        .def("total_number_tree_particles", &APR::total_number_tree_particles, "return number of interior tree particles")
+        .def("level_min", &APR::level_min, "return the minimum resolution level")
+        .def("level_max", &APR::level_max, "return the maximum resolution level")
+        .def("x_num", &APR::x_num, "level"_a)
+        .def("y_num", &APR::y_num, "level"_a)
+        .def("z_num", &APR::z_num, "level"_a)
+        .def("org_dims", &APR::org_dims, "returns the original image size in a specified dimension (y, x, z)", "dim"_a)
+        .def("shape", [](APR& self) { return py::make_tuple(self.org_dims(2), self.org_dims(1), self.org_dims(0)); })
+        .def("init_cuda", &APR::init_cuda, "copy access structures to GPU device", "with_tree"_a = true)
+        .def("cuda_device_bytes", [](APR& a) { return a.dev ? aprnet_device_bytes(a.dev) : (int64_t) 0; })
+        .def("plan", [](APR& a, int dl) { TORCH_CHECK(a.dev, "APR.init_cuda() must be called first");
+                                          check(aprnet_plan_build(a.dev, dl, nullptr), "plan"); }, "level_delta"_a,
+             "Build (and cache) the neighbour table of a level delta ahead of the first convolution")
+        .def("computational_ratio", &APR::computational_ratio)
+        .def(py::pickle(
+            [](APR& a) {
+                if (!a.initialized) throw std::runtime_error("Invalid state - APR not initialized");
+                return py::make_tuple(a.org_dims(0), a.org_dims(1), a.org_dims(2), a.name, to_array(a.row_ptr), to_array(a.y_vec),
+                                      to_array(a.tree_row_ptr), to_array(a.tree_y_vec));
+            },
+            [](py::tuple t) {
+                if (t.size() != 8) throw std::runtime_error("Error unpickling APR object - invalid state size");
+                auto a = std::make_unique<APR>();
+                a->init(t[2].cast<int>(), t[1].cast<int>(), t[0].cast<int>(), t[4].cast<py::array_t<int64_t>>(),
+                        t[5].cast<py::array_t<uint16_t>>(), t[6].cast<py::array_t<int64_t>>(), t[7].cast<py::array_t<uint16_t>>());
+                a->name = t[3].cast<std::string>();
+                return a;
+            }));
+    py::bind_vector<std::vector<APR*>>(data_containers, "APRPtrVector", py::module_local(false));
+
+    py::module aprnet = m.def_submodule("aprnet");
+    py::module utils = aprnet.def_submodule("utils");
+    utils.def("number_particles", [](APR& a, int dl) { return a.number_parts(dl); }, "apr"_a, "level_delta"_a);
+    utils.def("number_particles_after_pooling", [](APR& a, int dl) { return a.number_parts(dl + 1); }, "apr"_a, "level_delta"_a);
+    utils.def("number_particles_after_upsampling", [](APR& a, int dl) { return a.number_parts(dl - 1); }, "apr"_a, "level_delta"_a);
+    utils.def("number_parts", [](APR& a, int dl) { return a.number_parts(dl); }, "apr"_a, "level_delta"_a);
+
+    py::module cuda = aprnet.def_submodule("cuda");
+    cuda.def("maxpool_forward_cuda", &maxpool_forward_cuda, "aprs"_a, "input"_a, "level_delta"_a);
+    cuda.def("maxpool_backward_cuda", &maxpool_backward_cuda, "aprs"_a, "grad_output"_a, "max_indices"_a, "level_delta"_a);
+    cuda.def("conv111_forward", &conv111_forward, "aprs"_a, "input"_a, "weights"_a, "level_delta"_a);
+    cuda.def("conv111_backward", &conv111_backward, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a);
+    cuda.def("conv333_forward", &conv333_forward, "aprs"_a, "input"_a, "weights"_a, "level_delta"_a);
+    cuda.def("conv333_backward", &conv333_backward, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a);
+    cuda.def("upsample_const_forward", &upsample_const_forward, "aprs"_a, "input"_a, "level_delta"_a);
+    cuda.def("upsample_const_backward", &upsample_const_backward, "aprs"_a, "grad_output"_a, "level_delta"_a);
+    cuda.def("restrict_kernel333_forward", &restrict_kernel_333_forward, "weights"_a, "num_levels"_a);
+    cuda.def("restrict_kernel333_backward", &restrict_kernel_333_backward, "grad_weights_expanded"_a, "num_levels"_a);
+    // test / inspection hooks (not part of the reference interface)
+    cuda.def("fill_tree_mean", &fill_tree_mean_dl, "apr"_a, "input"_a, "level_delta"_a);
+    cuda.def("fill_tree_mean_backward", &fill_tree_mean_dl_backward, "apr"_a, "grad_input"_a, "grad_tree"_a, "level_delta"_a);
+    cuda.def("plan_nbr_table", &plan_nbr_table, "apr"_a, "level_delta"_a);
+    cuda.def("child_table", &child_table, "apr"_a);
+
+    py::module tree = m.def_submodule("tree");
+    tree.def("fill_tree_mean", [](APR& a, torch::Tensor x) { return fill_tree(a, x, false); }, "apr"_a, "parts"_a);
+    tree.def("fill_tree_max", [](APR& a, torch::Tensor x) { return fill_tree(a, x, true); }, "apr"_a, "parts"_a);
+}

@@ -1,0 +1,90 @@
+// Internal definitions shared by the CUDA translation units of libaprnet_b200.
+#pragma once
+
+#include <cstdint>
+#include <cstdio>
+#include <cstdarg>
+#include <string>
+#include <vector>
+#include <map>
+#include <cuda_runtime.h>
+#include "../../include/aprnet_b200.h"
+
+#define APRNET_MAX_LEVELS 20
+
+// Encoding of neighbour / child table entries:
+//   v >= 0 : index into the feature vector (APR particle, or upgraded tree node stored behind them)
+//   v == -1: nothing there (outside the domain) -> value 0
+//   v <= -2: tree node t = -2 - v (value comes from the tree scratch)
+#define APRNET_NONE (-1)
+__host__ __device__ inline int32_t aprnet_enc_tree(long long t) { return (int32_t) (-2 - t); }
+__host__ __device__ inline long long aprnet_dec_tree(int32_t v) { return -2 - (long long) v; }
+
+// Per-level geometry and index ranges; passed to kernels by value.
+struct LevelMeta {
+    int level_min, level_max;                    // particle levels; the tree spans level_min-1 .. level_max-1
+    int z_num[APRNET_MAX_LEVELS], x_num[APRNET_MAX_LEVELS], y_num[APRNET_MAX_LEVELS];
+    long long row_off[APRNET_MAX_LEVELS + 1];    // first particle row of each level
+    long long trow_off[APRNET_MAX_LEVELS + 1];   // first tree row of each level
+    long long lvl_begin[APRNET_MAX_LEVELS + 1];  // first particle index of each level ([l+1] = end of l)
+    long long tlvl_begin[APRNET_MAX_LEVELS + 1]; // first tree node index of each level
+};
+
+struct AprPlan {                 // cached per level_delta
+    int level_delta = 0;
+    long long n = 0;             // number of output locations (= number_parts)
+    long long tree_size = 0;
+    int32_t* nbr = nullptr;      // [27][n]
+};
+
+struct aprnet_apr {
+    int device = 0;
+    LevelMeta meta;
+    long long n_particles = 0, n_tree = 0, n_rows = 0, n_tree_rows = 0;
+    long long* row_ptr = nullptr;        // device
+    uint16_t* y = nullptr;
+    long long* tree_row_ptr = nullptr;
+    uint16_t* tree_y = nullptr;
+    int32_t* child = nullptr;            // [8][n_tree]
+    float* tree_scale = nullptr;         // [n_tree] weight of each child in its parent's mean
+    std::map<int, AprPlan> plans;
+    long long device_bytes = 0;
+
+    int cml(int dl) const { return meta.level_max - dl; }
+    long long number_parts(int dl) const {
+        const int c = cml(dl);
+        long long n = meta.lvl_begin[c + 1];
+        if (c <= meta.level_max - 1) n += meta.tlvl_begin[c + 1] - meta.tlvl_begin[c];
+        return n;
+    }
+    long long tree_size(int dl) const { return meta.tlvl_begin[cml(dl)]; }   // nodes of levels <= cml-1
+    long long tree_offset(int level) const { return meta.lvl_begin[level + 1] - meta.tlvl_begin[level]; }
+    bool valid_dl(int dl) const { return dl >= 0 && cml(dl) >= meta.level_min; }
+};
+
+void aprnet_set_error(const char* fmt, ...);
+
+#define APRNET_CUDA_CHECK(expr)                                                                     \
+    do {                                                                                            \
+        cudaError_t _e = (expr);                                                                    \
+        if (_e != cudaSuccess) {                                                                    \
+            aprnet_set_error("%s failed at %s:%d: %s", #expr, __FILE__, __LINE__, cudaGetErrorString(_e)); \
+            return APRNET_ERR_CUDA;                                                                 \
+        }                                                                                           \
+    } while (0)
+
+#define APRNET_LAUNCH_CHECK() APRNET_CUDA_CHECK(cudaGetLastError())
+
+#define APRNET_ARG_CHECK(cond, msg)                                                                 \
+    do { if (!(cond)) { aprnet_set_error("%s: %s", __func__, msg); return APRNET_ERR_ARG; } } while (0)
+
+inline int aprnet_ceil_div(long long a, long long b) { return (int) ((a + b - 1) / b); }
+
+// A contiguous range of output locations that shares one stencil slot.
+struct Segment { long long begin, end; int slot; int level; };
+// Segments of level_delta dl for a filter bank with `num_slots` slots: level l -> slot
+// min(cml - l, num_slots - 1); the upgraded tree nodes ride with the level-cml particles.
+// With merge=true, consecutive levels that share a slot are fused into one range (1x1x1 conv).
+std::vector<Segment> aprnet_segments(const aprnet_apr* apr, int dl, int num_slots, bool merge);
+
+const AprPlan* aprnet_get_plan(aprnet_apr* apr, int dl, cudaStream_t stream);

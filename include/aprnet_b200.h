@@ -1,0 +1,158 @@
+/*
+ * aprnet_b200 — C ABI of the B200 (sm_100a) particle-domain CNN operators.
+ *
+ * Drop-in boundary for the operator set that AdaptiveParticles/APR-CNN exposes to Python as
+ * `_pyaprwrapper.aprnet.cuda` (wrappers/pythonBind.cpp:162-181).  Every entry point takes plain
+ * pointers and sizes, returns 0 on success or a negative status (never aborts), launches on the
+ * stream it is given and performs no device-wide synchronisation and no allocation on the hot path:
+ * outputs and scratch buffers are owned by the caller.
+ *
+ * Conventions
+ *   - feature tensors are channel-major: element (c, p) of a tensor lives at base[c * ld + p], with
+ *     `ld` >= number of valid entries (the reference pads a batch to its largest APR,
+ *     pyapr/aprnet/cuda/src/wrap_conv_gpu.hpp:51);
+ *   - `level_delta` = number of poolings applied; the valid entries of a feature tensor are the APR
+ *     particles of levels <= level_max - level_delta followed by the tree nodes of that level
+ *     (pyapr/aprnet/src/helpers.hpp:86-101);
+ *   - `dtype` selects the arithmetic: APRNET_F32 or APRNET_F64 (the reference dispatches both,
+ *     wrap_conv_gpu.hpp:54);
+ *   - `stream` is a cudaStream_t passed as void*.
+ *   - all data pointers are DEVICE pointers unless the parameter name starts with `host_`.
+ */
+#ifndef APRNET_B200_H
+#define APRNET_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define APRNET_F32 0
+#define APRNET_F64 1
+
+#define APRNET_OK 0
+#define APRNET_ERR_ARG (-1)      /* bad argument (null pointer, level_delta out of range, size mismatch) */
+#define APRNET_ERR_CUDA (-2)     /* a CUDA runtime call failed; aprnet_last_error() has the text */
+#define APRNET_ERR_UNSUPPORTED (-3)
+
+typedef struct aprnet_apr aprnet_apr;
+
+/* Text of the last error raised on the calling thread. */
+const char* aprnet_last_error(void);
+
+/* ---- access structure ------------------------------------------------------------------------
+ * Replaces LibAPR's APR::init_cuda / gpuAPRHelper / gpuTreeHelper as used at
+ * pyapr/aprnet/cuda/src/wrap_conv_gpu.hpp:23-28 (device copies of level_xz_vec / xz_end_vec / y_vec
+ * for particles and tree).  Rows are numbered level-major, then z, then x; particles of row r are
+ * [row_ptr[r], row_ptr[r+1]) and `y` holds their ascending y coordinates.  `dims_zxy` holds
+ * (z_num, x_num, y_num) for levels 0..level_max.  Particle rows cover levels
+ * level_min..level_max, tree rows cover level_min-1..level_max-1.  All arguments are HOST arrays;
+ * they are copied to `device`.  Also builds the child table of the tree (cached). */
+int aprnet_apr_create(aprnet_apr** out, int level_min, int level_max, const int* host_dims_zxy,
+                      const int64_t* host_row_ptr, const uint16_t* host_y,
+                      const int64_t* host_tree_row_ptr, const uint16_t* host_tree_y, int device);
+void aprnet_apr_destroy(aprnet_apr* apr);
+
+/* pyapr/aprnet/src/helpers.hpp:86-110 (number_parts, number_parts_after_pooling/upsampling) */
+int64_t aprnet_number_parts(const aprnet_apr* apr, int level_delta);
+/* number of tree nodes of levels <= level_max - level_delta - 1: rows of the tree scratch that
+ * conv333 needs (pyapr/aprnet/cuda/src/wrap_conv_gpu.hpp:42-52) */
+int64_t aprnet_tree_size(const aprnet_apr* apr, int level_delta);
+int64_t aprnet_total_tree_nodes(const aprnet_apr* apr);
+/* bytes of device memory held by the handle (access arrays, child table, cached plans) */
+int64_t aprnet_device_bytes(const aprnet_apr* apr);
+
+/* Builds (once; cached in the handle) the neighbour table of `level_delta`: for each output
+ * location and each of the 27 stencil taps, which value fills that cell.  Replaces the per-call
+ * non-empty-row enumeration and dense-patch staging of the reference
+ * (pyapr/aprnet/cuda/src/nonempty_rows.cu:26-230, conv333_gpu.cu:63-118).  Called implicitly by the
+ * conv333 entry points; call it up front to keep allocation out of timed regions. */
+int aprnet_plan_build(aprnet_apr* apr, int level_delta, void* stream);
+/* Test hooks: copy the cached tables to host memory.  nbr: int32[27][N]; child: int32[8][T]. */
+int aprnet_plan_copy_nbr_table(aprnet_apr* apr, int level_delta, int32_t* host_out);
+int aprnet_copy_child_table(aprnet_apr* apr, int32_t* host_out);
+
+/* ---- tree fill -------------------------------------------------------------------------------
+ * pyapr/aprnet/cuda/src/fill_tree_gpu.hpp:15-32 (apply_fill_tree_mean / _backward); arithmetic of
+ * pyapr/aprnet/src/helpers.hpp:156-350.  tree is (C, ld_tree) with aprnet_tree_size() valid entries. */
+int aprnet_fill_tree_mean_forward(const aprnet_apr* apr, int level_delta, int dtype, int channels,
+                                  const void* input, int64_t ld_in, void* tree, int64_t ld_tree, void* stream);
+/* grad_input += adjoint(grad_tree); grad_tree is used as workspace (root-to-leaf accumulation). */
+int aprnet_fill_tree_mean_backward(const aprnet_apr* apr, int level_delta, int dtype, int channels,
+                                   void* grad_input, int64_t ld_in, void* grad_tree, int64_t ld_tree, void* stream);
+/* pyapr/tree/fill_tree.py:46-71 (fill_tree_max): every tree node = max over its descendants,
+ * level_delta 0, tree is (C, ld_tree) with aprnet_total_tree_nodes() valid entries. */
+int aprnet_fill_tree_max(const aprnet_apr* apr, int dtype, int channels, const void* input, int64_t ld_in,
+                         void* tree, int64_t ld_tree, void* stream);
+/* pyapr/tree/fill_tree.py:20-43 (fill_tree_mean): all tree nodes from the particles, level_delta 0 */
+int aprnet_fill_tree_mean_full(const aprnet_apr* apr, int dtype, int channels, const void* input, int64_t ld_in,
+                               void* tree, int64_t ld_tree, void* stream);
+
+/* ---- stencil restriction ---------------------------------------------------------------------
+ * pyapr/aprnet/cuda/src/restrict_gpu.hpp:25-32 (apply_restrict_kernel_333 / _backward).
+ * weights (S, Cout, Cin, 3,3,3) -> expanded (L, Cout, Cin, 3,3,3); backward is the transpose. */
+int aprnet_restrict333_forward(int dtype, int num_stencils, int num_levels, int64_t filters,
+                               const void* weights, void* expanded, void* stream);
+int aprnet_restrict333_backward(int dtype, int num_stencils, int num_levels, int64_t filters,
+                                const void* grad_expanded, void* grad_weights, void* stream);
+
+/* ---- 3x3x3 convolution -----------------------------------------------------------------------
+ * pyapr/aprnet/cuda/src/conv_gpu.hpp:74-96 (apply_conv333, apply_conv333_backward).
+ * weights: (num_slots, Cout, Cin, 27), level l uses slot min(cml - l, num_slots - 1).
+ * tree_scratch: (Cin, ld_tree) workspace, overwritten with fill_tree_mean(input). */
+int aprnet_conv333_forward(aprnet_apr* apr, int level_delta, int dtype, int cin, int cout, int num_slots,
+                           const void* input, int64_t ld_in, const void* weights,
+                           void* output, int64_t ld_out, void* tree_scratch, int64_t ld_tree, void* stream);
+/* grad_input (Cin, ld_in) must be zero-filled by the caller; grad_tree_scratch (Cin, ld_tree) is
+ * zero-filled by the call.  grad_output is (Cout, ld_out). */
+int aprnet_conv333_backward_input(aprnet_apr* apr, int level_delta, int dtype, int cin, int cout, int num_slots,
+                                  const void* grad_output, int64_t ld_out, const void* weights,
+                                  void* grad_input, int64_t ld_in, void* grad_tree_scratch, int64_t ld_tree,
+                                  void* stream);
+/* grad_weights (num_slots, Cout, Cin, 27) is ACCUMULATED into (so a batch loop sums, as the reference
+ * does).  tree_scratch must hold fill_tree_mean(input) (as left by the forward call, or recomputed with
+ * aprnet_fill_tree_mean_forward).  partial: workspace of aprnet_conv333_partial_elems() elements;
+ * block-local sums are written there and reduced in a fixed order (deterministic). */
+int64_t aprnet_conv333_partial_elems(int cin, int cout);
+int aprnet_conv333_backward_weights(aprnet_apr* apr, int level_delta, int dtype, int cin, int cout, int num_slots,
+                                    const void* input, int64_t ld_in, const void* tree_scratch, int64_t ld_tree,
+                                    const void* grad_output, int64_t ld_out, void* grad_weights,
+                                    void* partial, void* stream);
+
+/* ---- 1x1x1 convolution -----------------------------------------------------------------------
+ * pyapr/aprnet/cuda/src/conv_gpu.hpp:98-120 (apply_conv111 / _backward).  weights (S, Cout, Cin);
+ * level l uses stencil min(cml - l, S - 1), upgraded tree nodes use stencil 0. */
+int aprnet_conv111_forward(const aprnet_apr* apr, int level_delta, int dtype, int cin, int cout, int num_stencils,
+                           const void* input, int64_t ld_in, const void* weights, void* output, int64_t ld_out,
+                           void* stream);
+int aprnet_conv111_backward_input(const aprnet_apr* apr, int level_delta, int dtype, int cin, int cout,
+                                  int num_stencils, const void* grad_output, int64_t ld_out, const void* weights,
+                                  void* grad_input, int64_t ld_in, void* stream);
+int64_t aprnet_conv111_partial_elems(int cin, int cout);
+int aprnet_conv111_backward_weights(const aprnet_apr* apr, int level_delta, int dtype, int cin, int cout,
+                                    int num_stencils, const void* input, int64_t ld_in, const void* grad_output,
+                                    int64_t ld_out, void* grad_weights, void* partial, void* stream);
+
+/* ---- max pooling / constant up-sampling --------------------------------------------------------
+ * pyapr/aprnet/cuda/src/maxpool_gpu.hpp:24-40, upsample_constant_gpu.hpp:17-31.
+ * maxpool: level_delta -> level_delta + 1; max_indices are int64 positions in the input's particle
+ * axis; first maximum in the reference CPU's visiting order wins (pyapr/aprnet/src/maxpool.hpp:105-142). */
+int aprnet_maxpool_forward(const aprnet_apr* apr, int level_delta, int dtype, int channels,
+                           const void* input, int64_t ld_in, void* output, int64_t* max_indices, int64_t ld_out,
+                           void* stream);
+int aprnet_maxpool_backward(const aprnet_apr* apr, int level_delta, int dtype, int channels,
+                            const void* grad_output, const int64_t* max_indices, int64_t ld_out,
+                            void* grad_input, int64_t ld_in, void* stream);
+/* upsample: level_delta -> level_delta - 1 (level_delta must be > 0,
+ * pyapr/aprnet/cuda/src/wrap_upsample_const_gpu.hpp:36). */
+int aprnet_upsample_forward(const aprnet_apr* apr, int level_delta, int dtype, int channels,
+                            const void* input, int64_t ld_in, void* output, int64_t ld_out, void* stream);
+int aprnet_upsample_backward(const aprnet_apr* apr, int level_delta, int dtype, int channels,
+                             const void* grad_output, int64_t ld_out, void* grad_input, int64_t ld_in,
+                             void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* APRNET_B200_H */
