@@ -19,6 +19,7 @@
 #include <cmath>
 #include <cstdint>
 #include <memory>
+#include <sstream>
 #include <string>
 #include <vector>
 
@@ -507,6 +508,17 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
     cuda.def("fill_tree_mean_backward", &fill_tree_mean_dl_backward, "apr"_a, "grad_input"_a, "grad_tree"_a, "level_delta"_a);
     cuda.def("plan_nbr_table", &plan_nbr_table, "apr"_a, "level_delta"_a);
     cuda.def("child_table", &child_table, "apr"_a);
+    cuda.def("profile_enable", [](bool on) { aprnet_profile_enable(on ? 1 : 0); }, "on"_a,
+             "Bracket every kernel launch of the library with CUDA events (benchmark use)");
+    cuda.def("profile_read", []() {
+        std::string buf((size_t) 1 << 16, '\0');
+        aprnet_profile_read(&buf[0], (int64_t) buf.size());
+        py::dict out;
+        std::istringstream is(buf.c_str());
+        std::string name; long long calls; double ms;
+        while (is >> name >> calls >> ms) out[py::str(name)] = py::make_tuple(calls, ms);
+        return out;
+    }, "Return {kernel name: (launches, total milliseconds)} since the last read and clear the records");
 
     py::module tree = m.def_submodule("tree");
     tree.def("fill_tree_mean", [](APR& a, torch::Tensor x) { return fill_tree(a, x, false); }, "apr"_a, "parts"_a);

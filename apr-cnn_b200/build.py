@@ -51,7 +51,7 @@ def build_library(force=False, verbose=False):
                 if res.returncode:
                     raise RuntimeError("nvcc failed for " + cmd[-3])
     if jobs or force or _newer(out, objs):
-        subprocess.check_call([NVCC, "-shared", "-o", out] + objs + ["-lcudart"])
+        subprocess.check_call([NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", out] + objs + ["-lcudart"])
     return out
 
 

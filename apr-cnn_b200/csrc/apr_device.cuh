@@ -88,3 +88,12 @@ struct Segment { long long begin, end; int slot; int level; };
 std::vector<Segment> aprnet_segments(const aprnet_apr* apr, int dl, int num_slots, bool merge);
 
 const AprPlan* aprnet_get_plan(aprnet_apr* apr, int dl, cudaStream_t stream);
+
+// Optional per-kernel timing (aprnet_profile_enable): brackets a launch site with two CUDA events on
+// the launching stream.  Costs nothing when profiling is off.
+struct AprnetProfScope {
+    int slot;
+    cudaStream_t stream;
+    AprnetProfScope(const char* name, cudaStream_t st);
+    ~AprnetProfScope();
+};

@@ -22,6 +22,55 @@ void aprnet_set_error(const char* fmt, ...) {
 
 extern "C" const char* aprnet_last_error(void) { return g_last_error.c_str(); }
 
+// ---- per-kernel event timing -----------------------------------------------------------------
+namespace {
+struct ProfRecord { std::string name; cudaEvent_t start, stop; };
+bool g_prof_on = false;
+std::vector<ProfRecord> g_prof_records;
+}
+
+AprnetProfScope::AprnetProfScope(const char* name, cudaStream_t st) : slot(-1), stream(st) {
+    if (!g_prof_on) return;
+    ProfRecord r;
+    r.name = name;
+    if (cudaEventCreate(&r.start) != cudaSuccess || cudaEventCreate(&r.stop) != cudaSuccess) return;
+    cudaEventRecord(r.start, st);
+    g_prof_records.push_back(r);
+    slot = (int) g_prof_records.size() - 1;
+}
+
+AprnetProfScope::~AprnetProfScope() {
+    if (slot >= 0) cudaEventRecord(g_prof_records[slot].stop, stream);
+}
+
+extern "C" void aprnet_profile_enable(int on) { g_prof_on = on != 0; }
+
+extern "C" int64_t aprnet_profile_read(char* buf, int64_t buflen) {
+    std::map<std::string, std::pair<long long, double>> agg;
+    for (ProfRecord& r : g_prof_records) {
+        float ms = 0;
+        if (cudaEventSynchronize(r.stop) == cudaSuccess && cudaEventElapsedTime(&ms, r.start, r.stop) == cudaSuccess) {
+            agg[r.name].first += 1;
+            agg[r.name].second += ms;
+        }
+        cudaEventDestroy(r.start);
+        cudaEventDestroy(r.stop);
+    }
+    g_prof_records.clear();
+    std::string out;
+    for (auto& kv : agg) {
+        char line[256];
+        snprintf(line, sizeof(line), "%s %lld %.6f\n", kv.first.c_str(), kv.second.first, kv.second.second);
+        out += line;
+    }
+    if (buf && buflen > 0) {
+        const size_t n = std::min<size_t>(out.size(), (size_t) buflen - 1);
+        memcpy(buf, out.data(), n);
+        buf[n] = 0;
+    }
+    return (int64_t) out.size();
+}
+
 namespace {
 
 typedef long long ll;

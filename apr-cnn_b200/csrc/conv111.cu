@@ -130,7 +130,9 @@ int conv111_apply(const aprnet_apr* a, int dl, int n_in, int n_out, int S, const
     if (smem > 48 * 1024)
         APRNET_CUDA_CHECK(cudaFuncSetAttribute(conv111_kernel<T, OB, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     dim3 grid((unsigned) tiles, (unsigned) aprnet_ceil_div(n_out, OB));
+    { AprnetProfScope _prof("conv111", st);
     conv111_kernel<T, OB, TPB><<<grid, TPB, smem, st>>>(segs, in, ld_in, w, ws, wo, wi, out, ld_out, n_in, n_out);
+    }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
 }
@@ -145,8 +147,12 @@ int conv111_dw(const aprnet_apr* a, int dl, int cin, int cout, int S, const T* i
         const int nchunks = (int) std::min<ll>(DW_MAX_CHUNKS, (len + 1023) / 1024);
         const ll chunk_len = ((len + nchunks - 1) / nchunks + 31) / 32 * 32;
         dim3 grid((unsigned) nchunks, (unsigned) (aprnet_ceil_div(cout, 32) * aprnet_ceil_div(cin, 32)));
+        { AprnetProfScope _prof("conv111_dw", st);
         conv111_dw_partial_kernel<T><<<grid, 256, 0, st>>>(s.begin, s.end, chunk_len, in, ld_in, gout, ld_out, partial, cin, cout);
+        }
+        { AprnetProfScope _prof("conv111_dw_reduce", st);
         reduce_partial_kernel<T><<<aprnet_ceil_div(elems, 256), 256, 0, st>>>(partial, nchunks, elems, gw + (ll) s.slot * elems);
+        }
     }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;

@@ -305,12 +305,14 @@ template<> struct FwdCfg<double> { static constexpr int OB = 16, IB = 8, TPB = 1
 
 template<typename T, int OB, int IB, int TPB>
 int launch_forward(const SegTable& segs, const AprPlan* plan, const T* in, ll ld_in, const T* tree, ll ld_tree, const T* w,
-                   T* out, ll ld_out, int cin, int cout, cudaStream_t st) {
+                   T* out, ll ld_out, int cin, int cout, cudaStream_t st, const char* pname) {
     const size_t smem = (size_t) 27 * IB * OB * sizeof(T);
     auto kern = conv333_forward_kernel<T, OB, IB, TPB>;
     if (smem > 48 * 1024) APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     dim3 grid((unsigned) segs.tile_begin[segs.n], (unsigned) aprnet_ceil_div(cout, OB));
+    { AprnetProfScope _prof(pname, st);
     kern<<<grid, TPB, smem, st>>>(segs, plan->nbr, plan->n, in, ld_in, tree, ld_tree, w, out, ld_out, cin, cout);
+    }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
 }
@@ -323,23 +325,27 @@ int conv333_fwd(aprnet_apr* a, int dl, int cin, int cout, int slots, const T* in
     int rc = aprnet_fill_tree_mean_forward(a, dl, sizeof(T) == 4 ? APRNET_F32 : APRNET_F64, cin, in, ld_in, tree, ld_tree, st);
     if (rc) return rc;
     typedef FwdCfg<T> C;
+    char pname[64];
+    snprintf(pname, sizeof(pname), "conv333_fwd:ci%d:co%d:dl%d", cin, cout, dl);
     const SegTable segs = make_seg_table(aprnet_segments(a, dl, slots, false), C::TPB);
     if (segs.tile_begin[segs.n] == 0) return APRNET_OK;
     if (cout <= 4 && sizeof(T) == 4)
-        return launch_forward<T, 4, C::IB, C::TPB>(segs, plan, in, ld_in, tree, ld_tree, w, out, ld_out, cin, cout, st);
+        return launch_forward<T, 4, C::IB, C::TPB>(segs, plan, in, ld_in, tree, ld_tree, w, out, ld_out, cin, cout, st, pname);
     if (cout <= 16)
-        return launch_forward<T, 16, C::IB, C::TPB>(segs, plan, in, ld_in, tree, ld_tree, w, out, ld_out, cin, cout, st);
-    return launch_forward<T, C::OB, C::IB, C::TPB>(segs, plan, in, ld_in, tree, ld_tree, w, out, ld_out, cin, cout, st);
+        return launch_forward<T, 16, C::IB, C::TPB>(segs, plan, in, ld_in, tree, ld_tree, w, out, ld_out, cin, cout, st, pname);
+    return launch_forward<T, C::OB, C::IB, C::TPB>(segs, plan, in, ld_in, tree, ld_tree, w, out, ld_out, cin, cout, st, pname);
 }
 
 template<typename T, int OB, int IB, int TPB>
 int launch_backward_input(const SegTable& segs, const AprPlan* plan, const T* gout, ll ld_out, const T* w, T* gin, ll ld_in,
-                          T* gtree, ll ld_tree, int cin, int cout, cudaStream_t st) {
+                          T* gtree, ll ld_tree, int cin, int cout, cudaStream_t st, const char* pname) {
     const size_t smem = (size_t) 27 * IB * OB * sizeof(T);
     auto kern = conv333_backward_input_kernel<T, OB, IB, TPB>;
     if (smem > 48 * 1024) APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     dim3 grid((unsigned) segs.tile_begin[segs.n], (unsigned) aprnet_ceil_div(cin, IB));
+    { AprnetProfScope _prof(pname, st);
     kern<<<grid, TPB, smem, st>>>(segs, plan->nbr, plan->n, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout);
+    }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
 }
@@ -354,10 +360,12 @@ int conv333_bwd_input(aprnet_apr* a, int dl, int cin, int cout, int slots, const
         APRNET_CUDA_CHECK(cudaMemset2DAsync(gtree, (size_t) ld_tree * sizeof(T), 0, (size_t) ts * sizeof(T), (size_t) cin, st));
     constexpr int TPB = sizeof(T) == 4 ? 256 : 128;
     const SegTable segs = make_seg_table(aprnet_segments(a, dl, slots, false), TPB);
+    char pname[64];
+    snprintf(pname, sizeof(pname), "conv333_bwd_input:ci%d:co%d:dl%d", cin, cout, dl);
     if (segs.tile_begin[segs.n] > 0) {
         int rc;
-        if (cin <= 4) rc = launch_backward_input<T, 8, 4, TPB>(segs, plan, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout, st);
-        else rc = launch_backward_input<T, 8, 16, TPB>(segs, plan, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout, st);
+        if (cin <= 4) rc = launch_backward_input<T, 8, 4, TPB>(segs, plan, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout, st, pname);
+        else rc = launch_backward_input<T, 8, 16, TPB>(segs, plan, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout, st, pname);
         if (rc) return rc;
     }
     return aprnet_fill_tree_mean_backward(a, dl, sizeof(T) == 4 ? APRNET_F32 : APRNET_F64, cin, gin, ld_in, gtree, ld_tree, st);
@@ -373,12 +381,14 @@ inline int dw_max_ranges(int cin, int cout) {
 
 template<typename T, int IB, int OB, int OPT, int KCH, int TPB>
 int launch_dw(ll sb, ll se, int nranges, ll range_len, const AprPlan* plan, const T* in, ll ld_in, const T* tree, ll ld_tree,
-              const T* gout, ll ld_out, T* partial, int cin, int cout, cudaStream_t st) {
+              const T* gout, ll ld_out, T* partial, int cin, int cout, cudaStream_t st, const char* pname) {
     const size_t smem = (size_t) (27 * KCH * (IB + 1) + KCH * OB) * sizeof(T);
     auto kern = conv333_dw_partial_kernel<T, IB, OB, OPT, KCH, TPB>;
     if (smem > 48 * 1024) APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     dim3 grid((unsigned) nranges, (unsigned) (aprnet_ceil_div(cin, IB) * aprnet_ceil_div(cout, OB)));
+    { AprnetProfScope _prof(pname, st);
     kern<<<grid, TPB, smem, st>>>(sb, se, range_len, plan->nbr, plan->n, in, ld_in, tree, ld_tree, gout, ld_out, partial, cin, cout);
+    }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
 }
@@ -390,22 +400,26 @@ int conv333_bwd_weights(aprnet_apr* a, int dl, int cin, int cout, int slots, con
     if (!plan) return APRNET_ERR_CUDA;
     const ll elems = (ll) 27 * cin * cout;
     const int max_ranges = dw_max_ranges(cin, cout);
+    char pname[64];
+    snprintf(pname, sizeof(pname), "conv333_dw:ci%d:co%d:dl%d", cin, cout, dl);
     for (const Segment& s : aprnet_segments(a, dl, slots, false)) {
         const ll len = s.end - s.begin;
         const int nranges = (int) std::min<ll>(max_ranges, (len + 511) / 512);
         const ll range_len = (len + nranges - 1) / nranges;
         int rc;
         if (sizeof(T) == 8) {
-            rc = launch_dw<T, 16, 16, 1, 16, 256>(s.begin, s.end, nranges, range_len, plan, in, ld_in, tree, ld_tree, gout, ld_out, partial, cin, cout, st);
+            rc = launch_dw<T, 16, 16, 1, 16, 256>(s.begin, s.end, nranges, range_len, plan, in, ld_in, tree, ld_tree, gout, ld_out, partial, cin, cout, st, pname);
         } else if (cin >= 24) {
-            rc = launch_dw<T, 32, 32, 4, 32, 256>(s.begin, s.end, nranges, range_len, plan, in, ld_in, tree, ld_tree, gout, ld_out, partial, cin, cout, st);
+            rc = launch_dw<T, 32, 32, 4, 32, 256>(s.begin, s.end, nranges, range_len, plan, in, ld_in, tree, ld_tree, gout, ld_out, partial, cin, cout, st, pname);
         } else if (cin > 2) {
-            rc = launch_dw<T, 8, 32, 4, 32, 256>(s.begin, s.end, nranges, range_len, plan, in, ld_in, tree, ld_tree, gout, ld_out, partial, cin, cout, st);
+            rc = launch_dw<T, 8, 32, 4, 32, 256>(s.begin, s.end, nranges, range_len, plan, in, ld_in, tree, ld_tree, gout, ld_out, partial, cin, cout, st, pname);
         } else {
-            rc = launch_dw<T, 2, 32, 4, 64, 256>(s.begin, s.end, nranges, range_len, plan, in, ld_in, tree, ld_tree, gout, ld_out, partial, cin, cout, st);
+            rc = launch_dw<T, 2, 32, 4, 64, 256>(s.begin, s.end, nranges, range_len, plan, in, ld_in, tree, ld_tree, gout, ld_out, partial, cin, cout, st, pname);
         }
         if (rc) return rc;
+        { AprnetProfScope _prof("conv333_dw_reduce", st);
         reduce_partial_kernel<T><<<aprnet_ceil_div(elems, 256), 256, 0, st>>>(partial, nranges, elems, gw + (ll) s.slot * elems);
+        }
         APRNET_LAUNCH_CHECK();
     }
     return APRNET_OK;

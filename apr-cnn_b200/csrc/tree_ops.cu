@@ -190,8 +190,10 @@ int fill_tree_mean_fwd(const aprnet_apr* a, int dl, int C, const T* in, ll ld_in
     for (int lp = cml - 1; lp >= m.level_min - 1; --lp) {
         const ll tb = m.tlvl_begin[lp], te = m.tlvl_begin[lp + 1];
         if (te <= tb) continue;
+        { AprnetProfScope _prof("tree_mean_fwd", st);
         tree_mean_level_kernel<T><<<node_grid(te - tb, C), TPB, 0, st>>>(a->child, a->tree_scale, a->n_tree, tb, te, in,
                                                                           ld_in, tree, ld_tree, C, up, (dl > 0 && lp + 1 == cml) ? 1 : 0);
+        }
     }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
@@ -205,8 +207,10 @@ int fill_tree_mean_bwd(const aprnet_apr* a, int dl, int C, T* gin, ll ld_in, T* 
     for (int lp = m.level_min - 1; lp <= cml - 1; ++lp) {
         const ll tb = m.tlvl_begin[lp], te = m.tlvl_begin[lp + 1];
         if (te <= tb) continue;
+        { AprnetProfScope _prof("tree_mean_bwd", st);
         tree_mean_level_backward_kernel<T><<<node_grid(te - tb, C), TPB, 0, st>>>(
             a->child, a->tree_scale, a->n_tree, tb, te, gin, ld_in, gtree, ld_tree, C, up, (dl > 0 && lp + 1 == cml) ? 1 : 0);
+        }
     }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
@@ -218,7 +222,9 @@ int fill_tree_max_impl(const aprnet_apr* a, int C, const T* in, ll ld_in, T* tre
     for (int lp = m.level_max - 1; lp >= m.level_min - 1; --lp) {
         const ll tb = m.tlvl_begin[lp], te = m.tlvl_begin[lp + 1];
         if (te <= tb) continue;
+        { AprnetProfScope _prof("tree_max", st);
         tree_max_level_kernel<T><<<node_grid(te - tb, C), TPB, 0, st>>>(a->child, a->n_tree, tb, te, in, ld_in, tree, ld_tree, C);
+        }
     }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
@@ -234,8 +240,10 @@ int maxpool_fwd(const aprnet_apr* a, int dl, int C, const T* in, ll ld_in, T* ou
     const ll tb = m.tlvl_begin[cml - 1], te = m.tlvl_begin[cml];
     if (te > tb) {
         const ll up = (dl > 0) ? a->tree_offset(cml) : 0;
+        { AprnetProfScope _prof("maxpool_fwd", st);
         maxpool_kernel<T><<<node_grid(te - tb, C), TPB, 0, st>>>(a->child, a->n_tree, tb, te, a->tree_offset(cml - 1), in,
                                                                   ld_in, out, idx, ld_out, C, up);
+        }
         APRNET_LAUNCH_CHECK();
     }
     return APRNET_OK;
@@ -246,7 +254,9 @@ int maxpool_bwd(const aprnet_apr* a, int dl, int C, const T* gout, const long lo
     const ll mcount = a->number_parts(dl + 1);
     const ll nfixed = a->meta.lvl_begin[a->cml(dl)];
     if (mcount > 0) {
+        { AprnetProfScope _prof("maxpool_bwd", st);
         maxpool_backward_kernel<T><<<node_grid(mcount, C), TPB, 0, st>>>(gout, idx, ld_out, gin, ld_in, nfixed, mcount, C);
+        }
         APRNET_LAUNCH_CHECK();
     }
     return APRNET_OK;
@@ -262,8 +272,10 @@ int upsample_impl(const aprnet_apr* a, int dl, int C, const T* src, ll ld_src, T
     const ll tb = m.tlvl_begin[in_max], te = m.tlvl_begin[in_max + 1];
     if (te > tb) {
         const ll out_off = (out_max <= m.level_max - 1) ? a->tree_offset(out_max) : 0;
+        { AprnetProfScope _prof("upsample", st);
         upsample_kernel<T, BACKWARD><<<node_grid(te - tb, C), TPB, 0, st>>>(a->child, a->n_tree, tb, te, a->tree_offset(in_max),
                                                                              out_off, src, ld_src, dst, ld_dst, C);
+        }
         APRNET_LAUNCH_CHECK();
     }
     return APRNET_OK;

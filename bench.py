@@ -1,0 +1,375 @@
+#!/usr/bin/env python
+"""Benchmark of the particle-domain CNN hot path: APR U-Net forward + backward (+ SGD step).
+
+    python bench.py --gpus N --steps K --warmup W            # this implementation (CUDA, one rank per GPU)
+    python bench.py --impl reference --steps K --warmup W    # the reference's CPU operators on host cores
+
+One step = one training pass of the 4-level APR U-Net (base 32 channels, 2 convs per level, GroupNorm,
+ReLU, max-pool down / up-sample + concat up, 2 classes, cross-entropy against blob-interior labels)
+over one synthetic APR per GPU.  Inputs are seeded synthetic blob volumes (no dataset ships with the
+reference); metric = particles per second, summed over GPUs (weak scaling: one APR of the configured
+size per GPU, gradients all-reduced over NCCL).  Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "apr-cnn_b200"))
+
+import numpy as np
+import torch
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--volume", default="", help="z,x,y of the synthetic image (default: the headline config)")
+    ap.add_argument("--blobs", type=int, default=0)
+    ap.add_argument("--base", type=int, default=32)
+    ap.add_argument("--depth", type=int, default=3)
+    ap.add_argument("--dtype", default="f32", choices=["f32"])
+    ap.add_argument("--cpu-sample", default="64,128,128", help="volume of the bounded CPU-baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+HEADLINE_VOLUME = (512, 1024, 1024)      # configs[2] of BASELINE.json: 1024x1024x512 image, 5000 blobs
+HEADLINE_BLOBS = 5000
+
+
+def blob_count(volume, blobs):
+    if blobs > 0:
+        return blobs
+    dens = HEADLINE_BLOBS / float(np.prod(HEADLINE_VOLUME))
+    return max(4, int(round(dens * float(np.prod(volume)))))
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], tflops=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback")
+
+
+# ---------------------------------------------------------------------------------------------
+# workload construction
+# ---------------------------------------------------------------------------------------------
+def make_inputs(volume, blobs, seed, device):
+    """Seeded blob volume -> APR arrays, particle intensities (input channel) and labels."""
+    from pyapr import synthetic
+    img = synthetic.blob_image(volume, blobs, seed, device=device)
+    arrays = synthetic.apr_from_image(img)
+    feat = synthetic.sample_particles_from_image(img, arrays)
+    del img
+    labels = (feat > 300.0).astype(np.int64)          # blob interiors: well above background 100 + noise
+    feat = (feat - 100.0) / 500.0
+    return arrays, feat, labels
+
+
+class Clocks(threading.Thread):
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        super().__init__(daemon=True)
+        self.gpu_index = gpu_index
+        self.samples = []
+        self.proc = None
+
+    def run(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            for line in self.proc.stdout:
+                f = [s.strip() for s in line.split(",")]
+                if len(f) >= 9:
+                    self.samples.append(f)
+        except Exception:
+            pass
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+        self.join(timeout=2)
+        sm = sorted(float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit())
+        mx = [float(s[2]) for s in self.samples if s[2].replace(".", "").isdigit()]
+        reasons = set()
+        for s in self.samples:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None,
+                "reasons": sorted(reasons), "samples": len(self.samples)}
+
+
+def unet_conv_layers(base, depth):
+    """(kind, cin, cout, level_delta) of every convolution of the U-Net, forward order."""
+    w = [base * 2 ** i for i in range(depth + 1)]
+    layers = [("333", 1, w[0], 0), ("333", w[0], w[0], 0)]
+    for i in range(depth):
+        layers += [("333", w[i], w[i + 1], i + 1), ("333", w[i + 1], w[i + 1], i + 1)]
+    for i in reversed(range(depth)):
+        layers += [("111", w[i + 1], w[i + 1] // 2, i + 1), ("333", w[i + 1], w[i], i), ("333", w[i], w[i], i)]
+    layers.append(("111", w[0], 2, 0))
+    return layers
+
+
+def roofline_from_profile(prof, steps, nparts, ntree, peaks, layers):
+    """Roofline entry of the kernel that took the most time in the timed region.
+
+    Kernel names carry their shape: `conv333_fwd:ci32:co32:dl0`.  One "launch" below is one operator
+    call on one APR (the weight-gradient kernel runs once per level inside it; those launches are
+    summed).  Algorithmic work of one call: flops = 54 * cin * cout * N(dl);
+    bytes = (4 cin + 4 cout) * N + 2 N + 8 cin * T (tree scratch written and read once).  The bound is
+    the tensor pipe when flops/bytes exceeds the ridge of the measured peaks, HBM otherwise."""
+    if not prof:
+        return None
+    name, (calls, ms) = max(prof.items(), key=lambda kv: kv[1][1])
+    parts = name.split(":")
+    rf = {"kernel": name, "share_of_profiled": ms / sum(v[1] for v in prof.values())}
+    if parts[0].startswith("conv333") and len(parts) == 4:
+        cin, cout, dl = int(parts[1][2:]), int(parts[2][2:]), int(parts[3][2:])
+        n_ops = max(1, sum(1 for k, ci, co, d in layers if k == "333" and (ci, co, d) == (cin, cout, dl))) * steps
+        n, t = nparts[dl], ntree[dl]
+        flops = 54.0 * cin * cout * n
+        byts = (4.0 * cin + 4.0 * cout + 2.0) * n + 8.0 * cin * t
+        ridge = peaks["tflops"] * 1e12 / (peaks["hbm_gbs"] * 1e9)
+        sec = ms / n_ops * 1e-3
+        rf.update(launches_per_call=calls / n_ops, avg_ms=ms / n_ops)
+        if flops / byts > ridge:
+            ach = flops / sec / 1e12
+            rf.update(bound="tensor", achieved=ach, peak=peaks["tflops"], unit="TFLOP/s", frac=ach / peaks["tflops"])
+        else:
+            ach = byts / sec / 1e9
+            rf.update(bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"])
+        rf.update(algorithmic_flops=flops, algorithmic_bytes=byts, peak_source=peaks["source"], traffic=None)
+    return rf
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the reference's CPU operators on host cores (bounded sample)
+# ---------------------------------------------------------------------------------------------
+def run_cpu(args, steps, warmup):
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ref as ref_loader
+    import ref_modules
+    from apr_unet import APRUNet
+    ref_mod = ref_loader.load()
+    if ref_mod is None:
+        import apr_oracle
+        apr_oracle.build()
+    ops = ref_modules.make_ops(ref_mod)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    if ref_mod is not None:
+        ref_mod.set_num_threads(cores)
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    vol = tuple(int(v) for v in args.cpu_sample.split(","))
+    blobs = blob_count(vol, 0)
+    arrays, feat, labels = make_inputs(vol, blobs, 3000, "cpu")
+    apr = ref_modules.CpuApr(arrays, ref_mod)
+    torch.manual_seed(7)
+    model = APRUNet(ops, 1, 2, depth=args.depth, n_filters_base=args.base)
+    opt = torch.optim.SGD(model.parameters(), lr=1e-3)
+    x = torch.from_numpy(feat)[None, None].contiguous()
+    y = torch.from_numpy(labels)[None]
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        out = model(x, [apr])
+        loss = torch.nn.functional.cross_entropy(out, y)
+        loss.backward()
+        opt.step()
+        return float(loss)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    n = arrays.n_particles
+    return {"value": n / dt, "unit": "particles/s", "cores": cores, "kind": ops.kind,
+            "sample": "U-Net fwd+bwd+SGD, fp32, one APR from a %dx%dx%d (z,x,y) blob volume with %d blobs: %d particles, %.2f s/step, %d step(s)"
+                      % (vol[0], vol[1], vol[2], blobs, n, dt, steps), "ms_per_step": dt * 1e3, "particles": n}
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def run_gpu(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback for the b200 arm")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import pyapr
+    from pyapr.aprnet import cuda as ops
+    from _pyaprwrapper.aprnet import cuda as C
+    from apr_unet import APRUNet
+
+    volume = tuple(int(v) for v in args.volume.split(",")) if args.volume else HEADLINE_VOLUME
+    blobs = blob_count(volume, args.blobs)
+    t_setup = time.perf_counter()
+    arrays, feat, labels = make_inputs(volume, blobs, 3000 + rank, dev)
+    apr = pyapr.apr_from_arrays(arrays, "bench")
+    apr.init_cuda()
+    nparts = [int(pyapr.aprnet.utils.number_particles(apr, dl)) for dl in range(args.depth + 1)]
+    o_tree = []
+    for dl in range(args.depth + 1):
+        apr.plan(dl)
+        cml = arrays.level_max - dl
+        r = sum(arrays.dims[l][0] * arrays.dims[l][1] for l in range(0, cml))
+        o_tree.append(int(arrays.tree_row_ptr[r]))
+    torch.cuda.synchronize()
+    t_setup = time.perf_counter() - t_setup
+
+    torch.manual_seed(7)
+    model = APRUNet(ops, 1, 2, depth=args.depth, n_filters_base=args.base).to(dev)
+    opt = torch.optim.SGD(model.parameters(), lr=1e-3)
+    params = [p for p in model.parameters()]
+    x_host = torch.from_numpy(feat)[None, None].contiguous().pin_memory()
+    y_host = torch.from_numpy(labels)[None].contiguous().pin_memory()
+    x_dev, y_dev = x_host.to(dev), y_host.to(dev)
+    n_local = arrays.n_particles
+
+    def step(x, y):
+        opt.zero_grad(set_to_none=True)
+        out = model(x, [apr])
+        loss = torch.nn.functional.cross_entropy(out, y)
+        loss.backward()
+        if world > 1:
+            flat = torch.cat([p.grad.reshape(-1) for p in params])
+            dist.all_reduce(flat)
+            flat /= world
+            off = 0
+            for p in params:
+                p.grad.copy_(flat[off:off + p.numel()].view_as(p.grad))
+                off += p.numel()
+        opt.step()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(x_dev, y_dev)
+    barrier()
+
+    # ---- timed region: inputs resident in HBM --------------------------------------------------
+    clocks = Clocks(local_rank) if rank == 0 else None
+    if clocks:
+        clocks.start()
+        time.sleep(0.3)
+    C.profile_read()
+    C.profile_enable(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        loss = step(x_dev, y_dev)
+    e1.record()
+    barrier()
+    C.profile_enable(False)
+    ms = e0.elapsed_time(e1)
+    prof = C.profile_read()
+    clock_rec = clocks.stop() if clocks else None
+    loss_val = float(loss)
+
+    # ---- end-to-end: host buffers in, loss out, every step --------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            xd = x_host.to(dev, non_blocking=True)
+            yd = y_host.to(dev, non_blocking=True)
+            lv = step(xd, yd).item()
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms, e2e_ms if not args.no_e2e else 0.0, float(n_local)], dtype=torch.float64, device=dev)
+    if world > 1:
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        ms, e2e_ms_all, n_total = float(tmax[0]), float(tmax[1]), float(tsum[2])
+    else:
+        ms, e2e_ms_all, n_total = float(t[0]), float(t[1]), float(t[2])
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return None
+    peaks = load_peaks()
+    ms_per_step = ms / args.steps
+    launches = int(sum(v[0] for v in prof.values()))
+    out = {
+        "metric": "APR U-Net fwd+bwd particles/s", "value": n_total / (ms_per_step * 1e-3), "unit": "particles/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
+        "config": {"workload": "4-level APR U-Net (base %d, 2 convs/level, GroupNorm, ReLU, 2 classes) fwd+bwd+SGD on one APR per GPU from a "
+                               "seeded %dx%dx%d (z,x,y) uint16 blob volume, %d blobs" % (args.base, volume[0], volume[1], volume[2], blobs),
+                   "particles_per_gpu": n_local, "particles_by_level_delta": nparts, "tree_nodes_by_level_delta": o_tree,
+                   "parallelism": "one APR replica per GPU, gradient all-reduce (NCCL)" if world > 1 else "single GPU",
+                   "l2": "inputs larger than L2 (activations are GBs per layer)", "setup_s": t_setup, "loss": loss_val},
+        "gpu_launches": launches,
+        "clocks": clock_rec,
+        "kernels": {k: {"launches": v[0], "total_ms": v[1]} for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])[:12]},
+    }
+    if e2e_ms_all:
+        out["e2e"] = {"value": n_total / (e2e_ms_all / args.steps * 1e-3), "unit": "particles/s",
+                      "h2d_bytes_per_step": int(x_host.numel() * 4 + y_host.numel() * 8), "d2h_bytes_per_step": 4}
+    out["roofline"] = roofline_from_profile(prof, args.steps, nparts, o_tree, peaks, unet_conv_layers(args.base, args.depth))
+    if world == 1 and not args.no_cpu_baseline:
+        cb = run_cpu(args, 1, 1)
+        out["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if world > 1:
+        dist.destroy_process_group()
+    return out
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cb = run_cpu(args, max(1, args.steps), max(0, args.warmup))
+        out = {"impl": "reference", "metric": "APR U-Net fwd+bwd particles/s", "value": cb["value"], "unit": "particles/s",
+               "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step"],
+               "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+               "config": {"workload": "4-level APR U-Net fwd+bwd+SGD, reference CPU operators on host cores, bounded sample: " + cb["sample"]},
+               "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+               "e2e": {"value": cb["value"], "unit": "particles/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(out))
+        return
+    out = run_gpu(args)
+    if out is not None:
+        print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

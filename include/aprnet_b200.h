@@ -41,6 +41,13 @@ typedef struct aprnet_apr aprnet_apr;
 /* Text of the last error raised on the calling thread. */
 const char* aprnet_last_error(void);
 
+/* Optional per-kernel timing.  While enabled, every kernel launch made by this library is bracketed
+ * by two CUDA events on its stream.  aprnet_profile_read() waits for the recorded events, writes one
+ * line "name launches total_ms" per kernel into buf (NUL-terminated, truncated to buflen), clears the
+ * records and returns the untruncated length.  Not thread-safe; meant for benchmarks. */
+void aprnet_profile_enable(int on);
+int64_t aprnet_profile_read(char* buf, int64_t buflen);
+
 /* ---- access structure ------------------------------------------------------------------------
  * Replaces LibAPR's APR::init_cuda / gpuAPRHelper / gpuTreeHelper as used at
  * pyapr/aprnet/cuda/src/wrap_conv_gpu.hpp:23-28 (device copies of level_xz_vec / xz_end_vec / y_vec
@@ -141,6 +148,7 @@ int aprnet_conv111_backward_weights(const aprnet_apr* apr, int level_delta, int 
 int aprnet_maxpool_forward(const aprnet_apr* apr, int level_delta, int dtype, int channels,
                            const void* input, int64_t ld_in, void* output, int64_t* max_indices, int64_t ld_out,
                            void* stream);
+/* grad_input must be zero-filled by the caller (only the kept particles and the arg-max positions are written). */
 int aprnet_maxpool_backward(const aprnet_apr* apr, int level_delta, int dtype, int channels,
                             const void* grad_output, const int64_t* max_indices, int64_t ld_out,
                             void* grad_input, int64_t ld_in, void* stream);
