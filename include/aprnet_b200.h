@@ -141,6 +141,22 @@ int aprnet_conv111_backward_weights(const aprnet_apr* apr, int level_delta, int 
                                     int num_stencils, const void* input, int64_t ld_in, const void* grad_output,
                                     int64_t ld_out, void* grad_weights, void* partial, void* stream);
 
+/* No counterpart in the reference.  Same result as aprnet_conv111_backward_weights (float32 only,
+ * grad_weights (S, Cout, Cin) is accumulated into), for callers that cannot allocate device memory
+ * where they call this library — e.g. a host whose own arena owns the whole GPU, or a loop that cannot
+ * afford an allocation's device-wide synchronisation.  The block-partial sums live in a fixed 4 MiB
+ * array inside the library image (held by every GPU that loads the library until the process exits)
+ * instead of a caller workspace.  Limits and rules: cin * cout <= 262144, otherwise
+ * APRNET_ERR_UNSUPPORTED; calls that overlap on one GPU race on the shared array, so serialise them;
+ * the array keeps the previous call's contents (the call overwrites all it reads).  The first call on
+ * each device looks up the array's device address (with that device current); make that first call
+ * before starting any stream capture.  The call itself performs no allocation of any kind. */
+int aprnet_conv111_backward_weights_static(const aprnet_apr* apr, int level_delta, int cin, int cout,
+                                           int num_stencils, const float* input, int64_t ld_in,
+                                           const float* grad_output, int64_t ld_out, float* grad_weights,
+                                           void* stream);
+int64_t aprnet_static_scratch_bytes(void);
+
 /* ---- max pooling / constant up-sampling --------------------------------------------------------
  * pyapr/aprnet/cuda/src/maxpool_gpu.hpp:24-40, upsample_constant_gpu.hpp:17-31.
  * maxpool: level_delta -> level_delta + 1; max_indices are int64 positions in the input's particle
