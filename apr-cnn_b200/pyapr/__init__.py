@@ -27,6 +27,7 @@ from .data_containers import APR, APRPtrVector, apr_from_arrays  # noqa: E402
 from . import aprnet  # noqa: E402
 from . import tree  # noqa: E402
 from . import synthetic  # noqa: E402
+from . import sharding  # noqa: E402
 
 
 def cuda_enabled() -> bool:

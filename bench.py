@@ -226,6 +226,7 @@ def run_gpu(args):
     from pyapr.aprnet import cuda as ops
     from _pyaprwrapper.aprnet import cuda as C
     from apr_unet import APRUNet
+    from pyapr.sharding import allreduce_gradients
 
     volume = tuple(int(v) for v in args.volume.split(",")) if args.volume else HEADLINE_VOLUME
     blobs = blob_count(volume, args.blobs)
@@ -257,14 +258,7 @@ def run_gpu(args):
         out = model(x, [apr])
         loss = torch.nn.functional.cross_entropy(out, y)
         loss.backward()
-        if world > 1:
-            flat = torch.cat([p.grad.reshape(-1) for p in params])
-            dist.all_reduce(flat)
-            flat /= world
-            off = 0
-            for p in params:
-                p.grad.copy_(flat[off:off + p.numel()].view_as(p.grad))
-                off += p.numel()
+        allreduce_gradients(params, world)
         opt.step()
         return loss
 
