@@ -40,6 +40,8 @@ def parse_args():
     ap.add_argument("--cpu-sample", default="64,128,128", help="volume of the bounded CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--profile-step", action="store_true",
+                    help="after the timed region run one more step between cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     return ap.parse_args()
 
 
@@ -193,7 +195,7 @@ def run_cpu(args, steps, warmup):
         loss = torch.nn.functional.cross_entropy(out, y)
         loss.backward()
         opt.step()
-        return float(loss)
+        return float(loss.detach())
 
     for _ in range(warmup):
         step()
@@ -289,7 +291,14 @@ def run_gpu(args):
     ms = e0.elapsed_time(e1)
     prof = C.profile_read()
     clock_rec = clocks.stop() if clocks else None
-    loss_val = float(loss)
+    loss_val = float(loss.detach())
+
+    if args.profile_step:
+        barrier()
+        torch.cuda.profiler.start()
+        step(x_dev, y_dev)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
 
     # ---- end-to-end: host buffers in, loss out, every step --------------------------------------
     e2e = None

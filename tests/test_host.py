@@ -76,23 +76,34 @@ def test_operator_errors_without_gpu():
 
 
 def test_reference_unet_builds_on_these_modules():
-    """The reference's own model package constructs unchanged on top of pyapr.aprnet.cuda."""
-    path = "/root/reference/apr_models"
-    if not os.path.isdir(path):
+    """The reference's own U-Net source files construct unchanged on top of pyapr.aprnet.cuda.
+
+    The files are loaded directly (the package __init__ also pulls in the stardist models, which need
+    the absent `stardist` dependency)."""
+    base = "/root/reference/apr_models/apr_models/unet"
+    if not os.path.isdir(base):
         pytest.skip("reference checkout not present")
+    import importlib.util
+    import types
     import pyapr  # noqa: F401
-    sys.path.insert(0, path)
+    pkg = types.ModuleType("_ref_unet_pkg")
+    pkg.__path__ = [base]
+    sys.modules["_ref_unet_pkg"] = pkg
     try:
-        from apr_models.unet.unet_model import APRUNet
-    except ImportError as e:
-        pytest.skip("reference model package needs absent dependencies: %s" % e)
+        for name in ("unet_parts", "unet_model"):
+            spec = importlib.util.spec_from_file_location("_ref_unet_pkg." + name, os.path.join(base, name + ".py"))
+            mod = importlib.util.module_from_spec(spec)
+            sys.modules["_ref_unet_pkg." + name] = mod
+            spec.loader.exec_module(mod)
+        net = sys.modules["_ref_unet_pkg.unet_model"].APRUNet(1, 2, depth=3, n_filters_base=8)
     finally:
-        sys.path.remove(path)
-    net = APRUNet(1, 2, depth=3, n_filters_base=8)
+        for k in [k for k in sys.modules if k.startswith("_ref_unet_pkg")]:
+            del sys.modules[k]
     from apr_unet import APRUNet as Mine
     from pyapr.aprnet import cuda as ops
     mine = Mine(ops, 1, 2, depth=3, n_filters_base=8)
     assert sum(p.numel() for p in net.parameters()) == sum(p.numel() for p in mine.parameters())
+    assert sorted(tuple(p.shape) for p in net.parameters()) == sorted(tuple(p.shape) for p in mine.parameters())
 
 
 def test_shard_indices_partition_and_balance():
