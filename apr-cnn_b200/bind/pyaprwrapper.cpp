@@ -135,6 +135,9 @@ PYBIND11_MAKE_OPAQUE(std::vector<APR*>)
 
 namespace {
 
+// 0 = exact fp32/fp64 CUDA-core kernels; 1 = bf16 tensor-core path for float32 3x3x3 convolutions
+int g_conv_mode = 0;
+
 inline void check(int rc, const char* what) {
     TORCH_CHECK(rc == APRNET_OK, what, " failed (", rc, "): ", aprnet_last_error());
 }
@@ -195,10 +198,23 @@ torch::Tensor conv333_forward(std::vector<APR*>& aprs, torch::Tensor input, torc
     auto output = torch::empty({input.size(0), cout, n}, input.options());
     auto tree = torch::empty({cin, max_tree}, input.options());
     const int dt = dtype_id(input);
+    const bool tc = g_conv_mode == 1 && dt == APRNET_F32;
+    torch::Tensor ws;
+    if (tc) {
+        int64_t bytes = 256;
+        for (size_t i = 0; i < aprs.size(); ++i)
+            bytes = std::max<int64_t>(bytes, aprnet_conv333_tc_workspace_bytes(aprs[i]->handle(input), dl[i], (int) cin, (int) cout, (int) weights.size(0)));
+        ws = torch::empty({bytes}, input.options().dtype(torch::kUInt8));
+    }
     for (int64_t b = 0; b < input.size(0); ++b) {
-        check(aprnet_conv333_forward(aprs[b]->handle(input), dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(input, b), n,
-                                     weights.data_ptr(), row(output, b), n, tree.data_ptr(), max_tree, stream_of(input)),
-              "conv333_forward");
+        if (tc)
+            check(aprnet_conv333_forward_tc(aprs[b]->handle(input), dl[b], (int) cin, (int) cout, (int) weights.size(0), (const float*) row(input, b), n,
+                                            (const float*) weights.data_ptr(), (float*) row(output, b), n, (float*) tree.data_ptr(), max_tree,
+                                            ws.data_ptr(), stream_of(input)), "conv333_forward (tensor cores)");
+        else
+            check(aprnet_conv333_forward(aprs[b]->handle(input), dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(input, b), n,
+                                         weights.data_ptr(), row(output, b), n, tree.data_ptr(), max_tree, stream_of(input)),
+                  "conv333_forward");
         zero_padding(output, b, aprs[b]->number_parts(dl[b]));
     }
     return output;
@@ -226,12 +242,28 @@ std::vector<torch::Tensor> conv333_backward(std::vector<APR*>& aprs, torch::Tens
     auto partial = torch::empty({aprnet_conv333_partial_elems((int) cin, (int) cout)}, input.options());
     const int dt = dtype_id(input);
     void* st = stream_of(input);
+    const bool tc = g_conv_mode == 1 && dt == APRNET_F32;
+    torch::Tensor ws;
+    if (tc) {
+        int64_t bytes = 256;
+        for (size_t i = 0; i < aprs.size(); ++i)
+            bytes = std::max<int64_t>(bytes, aprnet_conv333_tc_workspace_bytes(aprs[i]->handle(input), dl[i], (int) cin, (int) cout, (int) weights.size(0)));
+        ws = torch::empty({bytes}, input.options().dtype(torch::kUInt8));
+    }
     for (int64_t b = 0; b < input.size(0); ++b) {
         aprnet_apr* h = aprs[b]->handle(input);
         check(aprnet_fill_tree_mean_forward(h, dl[b], dt, (int) cin, row(input, b), n, tree.data_ptr(), max_tree, st), "fill_tree_mean");
         check(aprnet_conv333_backward_weights(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(input, b), n,
                                               tree.data_ptr(), max_tree, row(grad_output, b), n, grad_weights.data_ptr(),
                                               partial.data_ptr(), st), "conv333_backward_weights");
+        if (tc) {
+            check(aprnet_conv333_backward_input_same_level_tc(h, dl[b], (int) cin, (int) cout, (int) weights.size(0), (const float*) row(grad_output, b), n,
+                                                              (const float*) weights.data_ptr(), (float*) row(grad_input, b), n, ws.data_ptr(), st),
+                  "conv333_backward_input (tensor cores)");
+            check(aprnet_conv333_backward_input_cross_level(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(grad_output, b), n,
+                                                            weights.data_ptr(), row(grad_input, b), n, grad_tree.data_ptr(), max_tree, st),
+                  "conv333_backward_input (cross-level)");
+        } else
         check(aprnet_conv333_backward_input(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(grad_output, b), n,
                                             weights.data_ptr(), row(grad_input, b), n, grad_tree.data_ptr(), max_tree, st),
               "conv333_backward_input");
@@ -508,6 +540,13 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
     cuda.def("fill_tree_mean_backward", &fill_tree_mean_dl_backward, "apr"_a, "grad_input"_a, "grad_tree"_a, "level_delta"_a);
     cuda.def("plan_nbr_table", &plan_nbr_table, "apr"_a, "level_delta"_a);
     cuda.def("child_table", &child_table, "apr"_a);
+    cuda.def("set_conv_precision", [](const std::string& mode) {
+        if (mode == "fp32") g_conv_mode = 0;
+        else if (mode == "bf16") g_conv_mode = 1;
+        else throw std::invalid_argument("conv precision must be 'fp32' or 'bf16'");
+    }, "mode"_a, "'fp32': exact CUDA-core kernels (default); 'bf16': tensor-core path for float32 3x3x3 convolutions (bf16 operands, fp32 accumulation)");
+    cuda.def("get_conv_precision", []() { return std::string(g_conv_mode == 1 ? "bf16" : "fp32"); });
+    cuda.def("tc_error_flag", []() { return aprnet_tc_error_flag(); });
     cuda.def("profile_enable", [](bool on) { aprnet_profile_enable(on ? 1 : 0); }, "on"_a,
              "Bracket every kernel launch of the library with CUDA events (benchmark use)");
     cuda.def("profile_read", []() {

@@ -121,7 +121,7 @@ template<typename T, int OB, int IB, int TPB>
 __global__ void __launch_bounds__(TPB) conv333_backward_input_kernel(SegTable segs, const int32_t* __restrict__ nbr, ll N,
                                                                      const T* __restrict__ gout, ll ld_out,
                                                                      const T* __restrict__ w, T* __restrict__ gin, ll ld_in,
-                                                                     T* __restrict__ gtree, ll ld_tree, int cin, int cout) {
+                                                                     T* __restrict__ gtree, ll ld_tree, int cin, int cout, int cross_only) {
     extern __shared__ unsigned char smem_raw[];
     T* wsm = reinterpret_cast<T*>(smem_raw);                      // [27][OB][IB]
     int seg = 0;
@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(TPB) conv333_backward_input_kernel(SegTable se
         for (int tap = 0; tap < 27; ++tap) {
             // gather from the same-level location at the mirrored offset
             const int32_t j = nbr[(ll) (26 - tap) * N + q];
-            if (j >= lo && j < hi) {
+            if (!cross_only && j >= lo && j < hi) {
                 const T* g = gout + (ll) o0 * ld_out + j;
                 const T* wt = wsm + tap * OB * IB;
                 for (int o = 0; o < ob; ++o) {
@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(TPB) conv333_backward_input_kernel(SegTable se
             }
         }
     }
-    if (active) {
+    if (active && !cross_only) {
 #pragma unroll
         for (int i = 0; i < IB; ++i)
             if (i0 + i < cin) atomicAdd(gin + (ll) (i0 + i) * ld_in + q, acc[i]);
@@ -338,13 +338,13 @@ int conv333_fwd(aprnet_apr* a, int dl, int cin, int cout, int slots, const T* in
 
 template<typename T, int OB, int IB, int TPB>
 int launch_backward_input(const SegTable& segs, const AprPlan* plan, const T* gout, ll ld_out, const T* w, T* gin, ll ld_in,
-                          T* gtree, ll ld_tree, int cin, int cout, cudaStream_t st, const char* pname) {
+                          T* gtree, ll ld_tree, int cin, int cout, cudaStream_t st, const char* pname, int cross_only) {
     const size_t smem = (size_t) 27 * IB * OB * sizeof(T);
     auto kern = conv333_backward_input_kernel<T, OB, IB, TPB>;
     if (smem > 48 * 1024) APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     dim3 grid((unsigned) segs.tile_begin[segs.n], (unsigned) aprnet_ceil_div(cin, IB));
     { AprnetProfScope _prof(pname, st);
-    kern<<<grid, TPB, smem, st>>>(segs, plan->nbr, plan->n, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout);
+    kern<<<grid, TPB, smem, st>>>(segs, plan->nbr, plan->n, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout, cross_only);
     }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
@@ -352,7 +352,7 @@ int launch_backward_input(const SegTable& segs, const AprPlan* plan, const T* go
 
 template<typename T>
 int conv333_bwd_input(aprnet_apr* a, int dl, int cin, int cout, int slots, const T* gout, ll ld_out, const T* w, T* gin,
-                      ll ld_in, T* gtree, ll ld_tree, cudaStream_t st) {
+                      ll ld_in, T* gtree, ll ld_tree, cudaStream_t st, int cross_only = 0) {
     const AprPlan* plan = aprnet_get_plan(a, dl, st);
     if (!plan) return APRNET_ERR_CUDA;
     const ll ts = a->tree_size(dl);
@@ -361,11 +361,11 @@ int conv333_bwd_input(aprnet_apr* a, int dl, int cin, int cout, int slots, const
     constexpr int TPB = sizeof(T) == 4 ? 256 : 128;
     const SegTable segs = make_seg_table(aprnet_segments(a, dl, slots, false), TPB);
     char pname[64];
-    snprintf(pname, sizeof(pname), "conv333_bwd_input:ci%d:co%d:dl%d", cin, cout, dl);
+    snprintf(pname, sizeof(pname), "%s:ci%d:co%d:dl%d", cross_only ? "conv333_bwd_cross" : "conv333_bwd_input", cin, cout, dl);
     if (segs.tile_begin[segs.n] > 0) {
         int rc;
-        if (cin <= 4) rc = launch_backward_input<T, 8, 4, TPB>(segs, plan, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout, st, pname);
-        else rc = launch_backward_input<T, 8, 16, TPB>(segs, plan, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout, st, pname);
+        if (cin <= 4) rc = launch_backward_input<T, 8, 4, TPB>(segs, plan, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout, st, pname, cross_only);
+        else rc = launch_backward_input<T, 8, 16, TPB>(segs, plan, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout, st, pname, cross_only);
         if (rc) return rc;
     }
     return aprnet_fill_tree_mean_backward(a, dl, sizeof(T) == 4 ? APRNET_F32 : APRNET_F64, cin, gin, ld_in, gtree, ld_tree, st);
@@ -470,4 +470,16 @@ extern "C" int aprnet_conv333_backward_weights(aprnet_apr* a, int dl, int dtype,
     cudaStream_t st = (cudaStream_t) stream;
     DISPATCH(dtype, conv333_bwd_weights<float>(a, dl, cin, cout, slots, (const float*) in, ld_in, (const float*) tree, ld_tree, (const float*) gout, ld_out, (float*) gw, (float*) partial, st),
              conv333_bwd_weights<double>(a, dl, cin, cout, slots, (const double*) in, ld_in, (const double*) tree, ld_tree, (const double*) gout, ld_out, (double*) gw, (double*) partial, st));
+}
+
+// Cross-level part of the input gradient only (coarser particles and tree nodes, then the tree
+// adjoint); the same-level part must already be in grad_input (tensor-core path).
+extern "C" int aprnet_conv333_backward_input_cross_level(aprnet_apr* a, int dl, int dtype, int cin, int cout, int slots,
+                                                         const void* gout, int64_t ld_out, const void* w, void* gin,
+                                                         int64_t ld_in, void* gtree, int64_t ld_tree, void* stream) {
+    CONV_CHECKS();
+    APRNET_ARG_CHECK(gout && w && gin && gtree, "null pointer");
+    cudaStream_t st = (cudaStream_t) stream;
+    DISPATCH(dtype, conv333_bwd_input<float>(a, dl, cin, cout, slots, (const float*) gout, ld_out, (const float*) w, (float*) gin, ld_in, (float*) gtree, ld_tree, st, 1),
+             conv333_bwd_input<double>(a, dl, cin, cout, slots, (const double*) gout, ld_out, (const double*) w, (double*) gin, ld_in, (double*) gtree, ld_tree, st, 1));
 }

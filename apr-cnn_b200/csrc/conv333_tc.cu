@@ -1,0 +1,482 @@
+// 3x3x3 particle convolution as an implicit GEMM on the 5th-generation tensor cores (tcgen05 + TMEM):
+// bf16 operands, fp32 accumulation.  sm_100a only.
+//
+// The reference has no tensor-core path at all (its kernels are CUDA-core code with atomics,
+// pyapr/aprnet/cuda/src/conv333_gpu.cu:11-579).  Formulation used here, per tile of 128 output
+// locations of one level:
+//
+//     D[128 x Cout] (TMEM, fp32)  +=  A_tap[128 x Cin] (smem, bf16)  *  W_tap[Cin x Cout] (smem, bf16)     for the 27 taps
+//
+// A_tap is the gather of the tap's neighbour rows through the cached neighbour table.  To make that a
+// plain row copy, the input (C, N) fp32 tensor (and the tree means) is first repacked into a
+// channels-last bf16 matrix [row][Cpad]; a neighbour is then Cpad*2 contiguous bytes that go from
+// global to shared memory with 16-byte cp.async copies, straight into the canonical K-major
+// no-swizzle operand layout ([8-channel chunk][row][8 channels], 8 rows x 16 B core matrices).  Weights
+// are packed once per call into the same canonical layout.  One elected thread issues tcgen05.mma;
+// completion is tracked with mbarriers (tcgen05.commit); accumulators are read back with tcgen05.ld
+// and written once, coalesced, to the fp32 (C, N) output.  Every wait is bounded: on expiry the block
+// raises an error flag in host-mapped memory, drains its copies, frees its TMEM and returns.
+//
+// The same kernel computes the same-level part of the input gradient (input = dO, weights transposed
+// and mirrored, neighbour entries masked to the location's own level).
+#include "apr_device.cuh"
+#include <cuda_bf16.h>
+#include <algorithm>
+
+namespace {
+
+typedef long long ll;
+constexpr int MAX_SEGS = APRNET_MAX_LEVELS;
+constexpr int TILE_M = 128;
+constexpr int STAGES = 4;
+constexpr unsigned SPIN_LIMIT = 1u << 22;
+
+struct SegTable {
+    int n;
+    ll begin[MAX_SEGS], end[MAX_SEGS];
+    int slot[MAX_SEGS];
+    int tile_begin[MAX_SEGS + 1];
+};
+
+inline SegTable make_seg_table(const std::vector<Segment>& segs, int tile) {
+    SegTable t;
+    t.n = (int) segs.size();
+    t.tile_begin[0] = 0;
+    for (int i = 0; i < t.n; ++i) {
+        t.begin[i] = segs[i].begin; t.end[i] = segs[i].end; t.slot[i] = segs[i].slot;
+        t.tile_begin[i + 1] = t.tile_begin[i] + aprnet_ceil_div(segs[i].end - segs[i].begin, tile);
+    }
+    return t;
+}
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template<int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.b32 %0, 1, 0, p;\n\t}\n" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait; returns false when the limit expired
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (unsigned it = 0; it < SPIN_LIMIT; ++it)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc], bf16 x bf16 -> fp32
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major, no swizzle: 8-row x 16-byte core matrices; LBO = byte
+// distance between the two 8-element K chunks of one MMA, SBO = byte distance between 8-row groups.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t) ((saddr >> 4) & 0x3FFF) | ((uint64_t) ((lbo >> 4) & 0x3FFF) << 16) |
+           ((uint64_t) ((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46);
+}
+// Instruction descriptor: D fp32, A/B bf16, both K-major, M = 128, N = n
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (TILE_M >> 4) << 24);
+}
+
+// ---- operand packing --------------------------------------------------------------------------------
+// rows [0, n): x[:, p]; rows [n, n + t): tree[:, p - n]; row n + t: zeros.  Channels padded to cpad.
+__global__ void pack_rows_bf16_kernel(const float* __restrict__ x, ll ld_x, ll n, const float* __restrict__ tree, ll ld_tree, ll t,
+                                      int c, int cpad, __nv_bfloat16* __restrict__ out) {
+    __shared__ float tile[32][33];
+    const ll r0 = (ll) blockIdx.x * 32;
+    const int c0 = blockIdx.y * 32;
+    const ll rows = n + t + 1;
+    {   // coalesced read along the row (particle) axis
+        const int cl = threadIdx.y;      // 0..7 -> 4 passes
+        for (int cc = cl; cc < 32; cc += 8) {
+            const ll r = r0 + threadIdx.x;
+            const int ch = c0 + cc;
+            float v = 0.f;
+            if (ch < c && r < n + t) v = (r < n) ? x[(ll) ch * ld_x + r] : tree[(ll) ch * ld_tree + (r - n)];
+            tile[cc][threadIdx.x] = v;
+        }
+    }
+    __syncthreads();
+    {   // write: thread -> (row, pair of channels), rows of the packed matrix are contiguous
+        const int tid = threadIdx.y * 32 + threadIdx.x;          // 256 threads
+        for (int e = tid; e < 32 * 16; e += 256) {
+            const int rr = e >> 4, cp = (e & 15) * 2;
+            const ll r = r0 + rr;
+            if (r < rows && c0 + cp < cpad) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(tile[cp][rr], tile[cp + 1][rr]);
+                *reinterpret_cast<__nv_bfloat162*>(out + r * cpad + c0 + cp) = v;
+            }
+        }
+    }
+}
+
+// Packed weights: [slot][tap][n_tile][k chunk j][n][8] bf16 (canonical K-major operand per (slot,tap,n_tile)).
+// forward:  B[n = co][k = ci] = w[slot][co][ci][tap]
+// backward: B[n = ci][k = co] = w[slot][co][ci][26 - tap]
+__global__ void pack_weights_bf16_kernel(const float* __restrict__ w, int slots, int cin, int cout, int backward,
+                                         int n_dim, int k_dim, int nt, int n_tiles, int kpad, __nv_bfloat16* __restrict__ out) {
+    const ll total = (ll) slots * 27 * n_tiles * (kpad / 8) * nt * 8;
+    for (ll e = (ll) blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (ll) gridDim.x * blockDim.x) {
+        ll r = e;
+        const int k8 = (int) (r % 8); r /= 8;
+        const int nn = (int) (r % nt); r /= nt;
+        const int j = (int) (r % (kpad / 8)); r /= (kpad / 8);
+        const int ntile = (int) (r % n_tiles); r /= n_tiles;
+        const int tap = (int) (r % 27); r /= 27;
+        const int slot = (int) r;
+        const int nidx = ntile * nt + nn, kidx = j * 8 + k8;
+        float v = 0.f;
+        if (nidx < n_dim && kidx < k_dim) {
+            const int co = backward ? kidx : nidx, ci = backward ? nidx : kidx;
+            const int tp = backward ? 26 - tap : tap;
+            v = w[(((ll) slot * cout + co) * cin + ci) * 27 + tp];
+        }
+        out[e] = __float2bfloat16(v);
+    }
+}
+
+// ---- main kernel -----------------------------------------------------------------------------------
+struct TcParams {
+    SegTable segs;
+    const int32_t* nbr; ll N;              // neighbour table [27][N]
+    const __nv_bfloat16* rows; int kpad;   // packed source rows [R][kpad]
+    ll tree_base, zero_row;                // row index of tree node 0 and of the zero row
+    const __nv_bfloat16* wp;               // packed weights
+    float* out; ll ld_out; int n_dim;      // output (n_dim, ld_out)
+    int n_tiles;
+    int same_level_only;                   // input-gradient mode: mask entries outside the tile's level
+    int* error_flag;
+};
+
+template<int NT, int KS>
+__global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
+    constexpr int A_BYTES = TILE_M * KS * 2;
+    constexpr int B_BYTES = NT * KS * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t IDESC = make_idesc(NT);
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char* stage_base = smem;                                            // STAGES * STAGE_BYTES
+    int32_t* idx_s = reinterpret_cast<int32_t*>(smem + STAGES * STAGE_BYTES);    // [27][128] source rows
+    uint64_t* bars = reinterpret_cast<uint64_t*>(idx_s + 27 * TILE_M);           // STAGES + 1 mbarriers
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + STAGES + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int kchunks = P.kpad / KS;
+    const int steps_per_tile = 27 * kchunks;
+
+    if (tid == 0) {
+        for (int i = 0; i <= STAGES; ++i) mbar_init(smem_u32(bars + i), 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), NT); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_d = *tmem_slot;
+
+    const int total_tiles = P.segs.tile_begin[P.segs.n] * P.n_tiles;
+    uint32_t gstep = 0;           // stages issued so far by this block (selects buffer and mbarrier phase)
+    uint32_t tiles_done = 0;
+    bool failed = false;
+
+    for (int work = blockIdx.x; work < total_tiles; work += gridDim.x) {
+        const int tile = work / P.n_tiles, ntile = work % P.n_tiles;
+        int seg = 0;
+        while (seg + 1 < P.segs.n && tile >= P.segs.tile_begin[seg + 1]) ++seg;
+        const ll lo = P.segs.begin[seg], hi = P.segs.end[seg];
+        const ll p = lo + (ll) (tile - P.segs.tile_begin[seg]) * TILE_M + tid;
+        const bool valid = p < hi;
+        const __nv_bfloat16* wtile = P.wp + ((ll) (P.segs.slot[seg] * 27) * P.n_tiles + ntile) * ((ll) P.kpad * NT);
+        const ll w_tap_stride = (ll) P.n_tiles * P.kpad * NT;
+
+        // source row of every tap for this thread's output location
+        for (int tap = 0; tap < 27; ++tap) {
+            ll r = P.zero_row;
+            if (valid) {
+                const int32_t q = P.nbr[(ll) tap * P.N + p];
+                if (P.same_level_only) { if (q >= lo && q < hi) r = q; }
+                else if (q >= 0) r = q;
+                else if (q != APRNET_NONE) r = P.tree_base + aprnet_dec_tree(q);
+            }
+            idx_s[tap * TILE_M + tid] = (int32_t) r;
+        }
+        // (each thread only reads back its own entries: no barrier needed here)
+
+        auto issue_loads = [&](int step) {
+            const int tap = step / kchunks, kc = step % kchunks;
+            const uint32_t buf = (gstep + (uint32_t) step) % STAGES;
+            unsigned char* a_s = stage_base + buf * STAGE_BYTES;
+            unsigned char* b_s = a_s + A_BYTES;
+            const __nv_bfloat16* src = P.rows + (ll) idx_s[tap * TILE_M + tid] * P.kpad + kc * KS;
+#pragma unroll
+            for (int j = 0; j < KS / 8; ++j) cp_async16(smem_u32(a_s + (j * TILE_M + tid) * 16), src + j * 8);
+            // weights of (tap, kc): chunks j in [kc*KS/8, (kc+1)*KS/8), each NT x 16 B, contiguous in global memory
+            const unsigned char* wsrc = reinterpret_cast<const unsigned char*>(wtile + (ll) tap * w_tap_stride + (ll) kc * KS * NT);
+            for (int e = tid; e < B_BYTES / 16; e += TILE_M) cp_async16(smem_u32(b_s + e * 16), wsrc + e * 16);
+        };
+
+        // prologue: fill STAGES-1 buffers (their previous readers, if any, must have finished)
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (s < steps_per_tile) {
+                const uint32_t g = gstep + s;
+                if (g >= STAGES) {
+                    const uint32_t use = g / STAGES;
+                    if (!mbar_wait(smem_u32(bars + g % STAGES), (use - 1) & 1)) failed = true;
+                }
+                issue_loads(s);
+            }
+            cp_async_commit();
+        }
+
+        for (int step = 0; step < steps_per_tile; ++step) {
+            cp_async_wait<STAGES - 2>();          // this thread's copies of `step` have landed
+            fence_proxy_async();                  // make them visible to the tensor-core (async) proxy
+            if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }     // uniform decision for the whole block
+            const uint32_t g = gstep + step;
+            if (tid == 0) {
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(stage_base + (g % STAGES) * STAGE_BYTES);
+                const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+                for (int k = 0; k < KS / 16; ++k) {
+                    const uint64_t da = make_desc(a_addr + k * 2 * (TILE_M * 16), TILE_M * 16, 128);
+                    const uint64_t db = make_desc(b_addr + k * 2 * (NT * 16), NT * 16, 128);
+                    umma_bf16(tmem_d, da, db, IDESC, (step > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(smem_u32(bars + g % STAGES));
+                if (step == steps_per_tile - 1) umma_commit(smem_u32(bars + STAGES));
+            }
+            // refill the buffer that the previous step's MMAs were reading
+            const int nxt = step + STAGES - 1;
+            if (nxt < steps_per_tile) {
+                const uint32_t gn = gstep + nxt;
+                if (gn >= STAGES) {
+                    const uint32_t use = gn / STAGES;
+                    if (!mbar_wait(smem_u32(bars + gn % STAGES), (use - 1) & 1)) failed = true;
+                }
+                if (!failed) issue_loads(nxt);
+            }
+            cp_async_commit();
+        }
+        gstep += steps_per_tile;
+        if (failed) break;
+
+        // epilogue: accumulators -> registers -> global (coalesced along the particle axis)
+        {
+            const bool ok = mbar_wait(smem_u32(bars + STAGES), tiles_done & 1);
+            if (__syncthreads_or(ok ? 0 : 1)) { failed = true; break; }
+        }
+        ++tiles_done;
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < NT; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_d + ((uint32_t) (warp * 32) << 16) + c0, r);
+            tmem_ld_wait();
+            if (valid) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int n = ntile * NT + c0 + j;
+                    if (n < P.n_dim) P.out[(ll) n * P.ld_out + p] = __uint_as_float(r[j]);
+                }
+            }
+        }
+        tc_fence_before();
+        __syncthreads();          // all TMEM reads done before the next tile's first MMA overwrites D
+    }
+
+    // teardown (also the error path): drain copies, release TMEM
+    cp_async_wait<0>();
+    if (failed && P.error_flag) *P.error_flag = 1;
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_d, NT);
+}
+
+// ---- host side ----------------------------------------------------------------------------------------
+int* g_error_flag_host = nullptr;     // host-mapped; written by kernels whose bounded waits expired
+int* g_error_flag_dev = nullptr;
+
+int ensure_error_flag() {
+    if (g_error_flag_host) return APRNET_OK;
+    APRNET_CUDA_CHECK(cudaHostAlloc((void**) &g_error_flag_host, sizeof(int), cudaHostAllocMapped));
+    *g_error_flag_host = 0;
+    APRNET_CUDA_CHECK(cudaHostGetDevicePointer((void**) &g_error_flag_dev, g_error_flag_host, 0));
+    return APRNET_OK;
+}
+
+inline int pad_to(int v, int m) { return (v + m - 1) / m * m; }
+inline int pick_nt(int n) { return n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256)); }
+
+struct TcGeom { int kpad, ks, nt, n_tiles; size_t rows_bytes, w_bytes; };
+
+TcGeom tc_geometry(ll rows, int k_dim, int n_dim, int slots) {
+    TcGeom g;
+    g.kpad = pad_to(k_dim, 16);
+    g.ks = (g.kpad % 32 == 0) ? 32 : 16;
+    g.nt = pick_nt(n_dim);
+    g.n_tiles = (n_dim + g.nt - 1) / g.nt;
+    g.rows_bytes = ((size_t) rows * g.kpad * 2 + 255) / 256 * 256;
+    g.w_bytes = ((size_t) slots * 27 * g.n_tiles * g.kpad * g.nt * 2 + 255) / 256 * 256;
+    return g;
+}
+
+template<int NT, int KS>
+int launch_tc(const TcParams& P, int total_tiles, cudaStream_t st, const char* pname) {
+    const size_t smem = (size_t) STAGES * (TILE_M * KS * 2 + NT * KS * 2) + 27 * TILE_M * 4 + (STAGES + 1) * 8 + 16;
+    auto kern = conv333_tc_kernel<NT, KS>;
+    APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int per_sm = std::max(1, std::min(std::min(4, 512 / NT), (int) (200 * 1024 / smem)));
+    const int grid = std::min(total_tiles, sms * per_sm);
+    { AprnetProfScope _prof(pname, st);
+    kern<<<grid, TILE_M, smem, st>>>(P);
+    }
+    APRNET_LAUNCH_CHECK();
+    return APRNET_OK;
+}
+
+int dispatch_tc(const TcParams& P, const TcGeom& g, int total_tiles, cudaStream_t st, const char* pname) {
+#define TC_CASE(NT_, KS_) if (g.nt == NT_ && g.ks == KS_) return launch_tc<NT_, KS_>(P, total_tiles, st, pname);
+    TC_CASE(32, 16) TC_CASE(32, 32) TC_CASE(64, 16) TC_CASE(64, 32) TC_CASE(128, 16) TC_CASE(128, 32) TC_CASE(256, 16) TC_CASE(256, 32)
+#undef TC_CASE
+    aprnet_set_error("conv333 tensor-core path: unsupported tile geometry nt=%d ks=%d", g.nt, g.ks);
+    return APRNET_ERR_UNSUPPORTED;
+}
+
+int run_pack_rows(const float* x, ll ld_x, ll n, const float* tree, ll ld_tree, ll t, int c, int cpad, __nv_bfloat16* out, cudaStream_t st) {
+    dim3 grid((unsigned) aprnet_ceil_div(n + t + 1, 32), (unsigned) aprnet_ceil_div(cpad, 32));
+    { AprnetProfScope _prof("pack_rows_bf16", st);
+    pack_rows_bf16_kernel<<<grid, dim3(32, 8), 0, st>>>(x, ld_x, n, tree, ld_tree, t, c, cpad, out);
+    }
+    APRNET_LAUNCH_CHECK();
+    return APRNET_OK;
+}
+
+} // namespace
+
+extern "C" int aprnet_tc_error_flag(void) { return g_error_flag_host ? *g_error_flag_host : 0; }
+
+extern "C" int64_t aprnet_conv333_tc_workspace_bytes(const aprnet_apr* a, int dl, int cin, int cout, int slots) {
+    if (!a || !a->valid_dl(dl)) return -1;
+    const ll rows_f = a->number_parts(dl) + a->tree_size(dl) + 1;
+    const TcGeom f = tc_geometry(rows_f, cin, cout, slots);
+    const TcGeom b = tc_geometry(a->number_parts(dl) + 1, cout, cin, slots);
+    return (int64_t) std::max(f.rows_bytes + f.w_bytes, b.rows_bytes + b.w_bytes);
+}
+
+// forward: out = conv(in) with bf16 operands / fp32 accumulation; tree_scratch receives the fp32 tree means
+extern "C" int aprnet_conv333_forward_tc(aprnet_apr* a, int dl, int cin, int cout, int slots, const float* in, int64_t ld_in,
+                                         const float* w, float* out, int64_t ld_out, float* tree, int64_t ld_tree,
+                                         void* workspace, void* stream) {
+    APRNET_ARG_CHECK(a && a->valid_dl(dl) && cin > 0 && cout > 0 && slots > 0 && in && w && out && tree && workspace, "bad argument");
+    APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl) && ld_tree >= a->tree_size(dl), "leading dimension too small");
+    cudaStream_t st = (cudaStream_t) stream;
+    int rc = ensure_error_flag();
+    if (rc) return rc;
+    if (*g_error_flag_host) { aprnet_set_error("a previous tensor-core kernel gave up waiting on a barrier"); return APRNET_ERR_CUDA; }
+    const AprPlan* plan = aprnet_get_plan(a, dl, st);
+    if (!plan) return APRNET_ERR_CUDA;
+    rc = aprnet_fill_tree_mean_forward(a, dl, APRNET_F32, cin, in, ld_in, tree, ld_tree, st);
+    if (rc) return rc;
+    const ll n = plan->n, t = plan->tree_size;
+    const TcGeom g = tc_geometry(n + t + 1, cin, cout, slots);
+    __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(workspace);
+    __nv_bfloat16* wp = reinterpret_cast<__nv_bfloat16*>((char*) workspace + g.rows_bytes);
+    rc = run_pack_rows(in, ld_in, n, tree, ld_tree, t, cin, g.kpad, rows, st);
+    if (rc) return rc;
+    { AprnetProfScope _prof("pack_weights_bf16", st);
+    pack_weights_bf16_kernel<<<std::min(1024, aprnet_ceil_div((ll) slots * 27 * g.n_tiles * g.kpad * g.nt, 256)), 256, 0, st>>>(
+        w, slots, cin, cout, 0, cout, cin, g.nt, g.n_tiles, g.kpad, wp);
+    }
+    APRNET_LAUNCH_CHECK();
+    TcParams P;
+    P.segs = make_seg_table(aprnet_segments(a, dl, slots, false), TILE_M);
+    P.nbr = plan->nbr; P.N = n; P.rows = rows; P.kpad = g.kpad; P.tree_base = n; P.zero_row = n + t;
+    P.wp = wp; P.out = out; P.ld_out = ld_out; P.n_dim = cout; P.n_tiles = g.n_tiles; P.same_level_only = 0;
+    P.error_flag = g_error_flag_dev;
+    const int total = P.segs.tile_begin[P.segs.n] * g.n_tiles;
+    if (total == 0) return APRNET_OK;
+    char pname[64];
+    snprintf(pname, sizeof(pname), "conv333_tc_fwd:ci%d:co%d:dl%d", cin, cout, dl);
+    return dispatch_tc(P, g, total, st, pname);
+}
+
+// same-level part of the input gradient: gin[ci][q] = sum_taps sum_co W[co][ci][tap] * dO[co][mirror neighbour]
+// (written, not accumulated; the cross-level part and the tree adjoint are added by the caller afterwards)
+extern "C" int aprnet_conv333_backward_input_same_level_tc(aprnet_apr* a, int dl, int cin, int cout, int slots, const float* gout,
+                                                           int64_t ld_out, const float* w, float* gin, int64_t ld_in,
+                                                           void* workspace, void* stream) {
+    APRNET_ARG_CHECK(a && a->valid_dl(dl) && cin > 0 && cout > 0 && slots > 0 && gout && w && gin && workspace, "bad argument");
+    APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl), "leading dimension too small");
+    cudaStream_t st = (cudaStream_t) stream;
+    int rc = ensure_error_flag();
+    if (rc) return rc;
+    if (*g_error_flag_host) { aprnet_set_error("a previous tensor-core kernel gave up waiting on a barrier"); return APRNET_ERR_CUDA; }
+    const AprPlan* plan = aprnet_get_plan(a, dl, st);
+    if (!plan) return APRNET_ERR_CUDA;
+    const ll n = plan->n;
+    const TcGeom g = tc_geometry(n + 1, cout, cin, slots);
+    __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(workspace);
+    __nv_bfloat16* wp = reinterpret_cast<__nv_bfloat16*>((char*) workspace + g.rows_bytes);
+    rc = run_pack_rows(gout, ld_out, n, nullptr, 0, 0, cout, g.kpad, rows, st);
+    if (rc) return rc;
+    { AprnetProfScope _prof("pack_weights_bf16", st);
+    pack_weights_bf16_kernel<<<std::min(1024, aprnet_ceil_div((ll) slots * 27 * g.n_tiles * g.kpad * g.nt, 256)), 256, 0, st>>>(
+        w, slots, cin, cout, 1, cin, cout, g.nt, g.n_tiles, g.kpad, wp);
+    }
+    APRNET_LAUNCH_CHECK();
+    TcParams P;
+    P.segs = make_seg_table(aprnet_segments(a, dl, slots, false), TILE_M);
+    P.nbr = plan->nbr; P.N = n; P.rows = rows; P.kpad = g.kpad; P.tree_base = n; P.zero_row = n;
+    P.wp = wp; P.out = gin; P.ld_out = ld_in; P.n_dim = cin; P.n_tiles = g.n_tiles; P.same_level_only = 1;
+    P.error_flag = g_error_flag_dev;
+    const int total = P.segs.tile_begin[P.segs.n] * g.n_tiles;
+    if (total == 0) return APRNET_OK;
+    char pname[64];
+    snprintf(pname, sizeof(pname), "conv333_tc_bwd_gather:ci%d:co%d:dl%d", cin, cout, dl);
+    return dispatch_tc(P, g, total, st, pname);
+}

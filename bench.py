@@ -36,7 +36,8 @@ def parse_args():
     ap.add_argument("--blobs", type=int, default=0)
     ap.add_argument("--base", type=int, default=32)
     ap.add_argument("--depth", type=int, default=3)
-    ap.add_argument("--dtype", default="f32", choices=["f32"])
+    ap.add_argument("--dtype", default="bf16", choices=["f32", "bf16"],
+                    help="arithmetic of the 3x3x3 convolutions: exact fp32 CUDA-core kernels, or bf16 tensor-core contraction with fp32 accumulation")
     ap.add_argument("--cpu-sample", default="64,128,128", help="volume of the bounded CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -142,7 +143,7 @@ def roofline_from_profile(prof, steps, nparts, ntree, peaks, layers):
     name, (calls, ms) = max(prof.items(), key=lambda kv: kv[1][1])
     parts = name.split(":")
     rf = {"kernel": name, "share_of_profiled": ms / sum(v[1] for v in prof.values())}
-    if parts[0].startswith("conv333") and len(parts) == 4:
+    if parts[0].startswith("conv333") and len(parts) == 4 and parts[1].startswith("ci"):
         cin, cout, dl = int(parts[1][2:]), int(parts[2][2:]), int(parts[3][2:])
         n_ops = max(1, sum(1 for k, ci, co, d in layers if k == "333" and (ci, co, d) == (cin, cout, dl))) * steps
         n, t = nparts[dl], ntree[dl]
@@ -230,6 +231,7 @@ def run_gpu(args):
     from apr_unet import APRUNet
     from pyapr.sharding import allreduce_gradients
 
+    C.set_conv_precision("bf16" if args.dtype == "bf16" else "fp32")
     volume = tuple(int(v) for v in args.volume.split(",")) if args.volume else HEADLINE_VOLUME
     blobs = blob_count(volume, args.blobs)
     t_setup = time.perf_counter()

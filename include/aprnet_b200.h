@@ -127,6 +127,28 @@ int aprnet_conv333_backward_weights(aprnet_apr* apr, int level_delta, int dtype,
                                     const void* grad_output, int64_t ld_out, void* grad_weights,
                                     void* partial, void* stream);
 
+/* ---- 3x3x3 convolution on the tensor cores (bf16 operands, fp32 accumulation) ------------------
+ * No counterpart in the reference (its kernels are CUDA-core only).  Same contract as
+ * aprnet_conv333_forward for float32 tensors; results differ by the bf16 rounding of inputs and
+ * weights (relative error <= 2e-2).  `workspace` needs aprnet_conv333_tc_workspace_bytes() bytes,
+ * 256-byte aligned.  Waits inside the kernels are bounded; aprnet_tc_error_flag() becomes non-zero
+ * if one ever expired, and later calls then fail with APRNET_ERR_CUDA. */
+int64_t aprnet_conv333_tc_workspace_bytes(const aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots);
+int aprnet_conv333_forward_tc(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
+                              const float* input, int64_t ld_in, const float* weights, float* output, int64_t ld_out,
+                              float* tree_scratch, int64_t ld_tree, void* workspace, void* stream);
+/* Input gradient in two parts: the taps whose source is a location of the same level are a gather
+ * (tensor cores; WRITES grad_input), the taps whose source is a coarser particle or a tree node are
+ * scattered with atomicAdd on top and followed by the tree adjoint (CUDA cores). */
+int aprnet_conv333_backward_input_same_level_tc(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
+                                                const float* grad_output, int64_t ld_out, const float* weights,
+                                                float* grad_input, int64_t ld_in, void* workspace, void* stream);
+int aprnet_conv333_backward_input_cross_level(aprnet_apr* apr, int level_delta, int dtype, int cin, int cout, int num_slots,
+                                              const void* grad_output, int64_t ld_out, const void* weights,
+                                              void* grad_input, int64_t ld_in, void* grad_tree_scratch, int64_t ld_tree,
+                                              void* stream);
+int aprnet_tc_error_flag(void);
+
 /* ---- 1x1x1 convolution -----------------------------------------------------------------------
  * pyapr/aprnet/cuda/src/conv_gpu.hpp:98-120 (apply_conv111 / _backward).  weights (S, Cout, Cin);
  * level l uses stencil min(cml - l, S - 1), upgraded tree nodes use stencil 0. */

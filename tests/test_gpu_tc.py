@@ -1,0 +1,65 @@
+"""Tensor-core (bf16 operands, fp32 accumulation) 3x3x3 convolution against the CPU oracle.
+
+Inputs and weights are chosen bf16-representable, so the only differences from the float64 oracle are
+fp32 accumulation order and the bf16 rounding of the tree means: the check is much tighter (5e-3) than
+the bound the bf16 path has to meet for arbitrary inputs (relative error <= 2e-2), which is checked
+separately with unrounded inputs.
+"""
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+def bf16_round(a):
+    return torch.from_numpy(np.asarray(a, dtype=np.float32)).to(torch.bfloat16).to(torch.float32).numpy()
+
+
+@pytest.fixture()
+def bf16_mode():
+    from _pyaprwrapper.aprnet import cuda as C
+    C.set_conv_precision("bf16")
+    yield C
+    C.set_conv_precision("fp32")
+    assert C.tc_error_flag() == 0, "a tensor-core kernel gave up waiting on a barrier"
+
+
+CHANNELS = [(3, 4, 2), (32, 32, 2), (33, 33, 3), (64, 48, 1), (16, 136, 2), (1, 32, 2), (72, 260, 1)]
+
+
+@pytest.mark.parametrize("cin,cout,nst", CHANNELS)
+@pytest.mark.parametrize("name", ["blob", "odd", "ref_shape"])
+def test_conv333_tensor_core_path(name, cin, cout, nst, oracle, bf16_mode):
+    import pyapr
+    from _pyaprwrapper.data_containers import APRPtrVector
+    C = bf16_mode
+    dev = torch.device("cuda:0")
+    a = H.arrays(name) if name in H.APR_CASES else H.blob_arrays()
+    apr = pyapr.apr_from_arrays(a, name)
+    apr.init_cuda()
+    o = oracle.OracleAPR(a)
+    L = a.level_max - a.level_min + 1
+    rng = np.random.RandomState(3)
+    for dl in range(0, min(H.max_dl(a), 2) + 1):
+        n = o.number_parts(dl)
+        ld = torch.full((1,), dl, dtype=torch.int32)
+        for exact_inputs in (True, False):
+            x = rng.rand(cin, n).astype(np.float32)
+            w = (rng.randn(L, cout, cin, 3, 3, 3) / np.sqrt(27 * cin)).astype(np.float32)
+            go = rng.randn(cout, n).astype(np.float32)
+            if exact_inputs:
+                x, w, go = bf16_round(x), bf16_round(w), bf16_round(go)
+            xt = torch.from_numpy(x).to(dev)[None].contiguous()
+            wt = torch.from_numpy(w).to(dev)
+            got = torch.from_numpy(go).to(dev)[None].contiguous()
+            out = C.conv333_forward(APRPtrVector([apr]), xt, wt, ld)
+            gi, gw = C.conv333_backward(APRPtrVector([apr]), xt, wt, got, ld)
+            want = o.conv333_forward(x.astype(np.float64), w.astype(np.float64), dl)
+            gi_ref, gw_ref = o.conv333_backward(x.astype(np.float64), w.astype(np.float64), go.astype(np.float64), dl)
+            tol_out, tol_gi = (5e-3, 1e-4) if exact_inputs else (2e-2, 2e-2)
+            assert H.rel_err(H.t2n(out[0]), want) <= tol_out, (name, dl, exact_inputs)
+            assert H.rel_err(H.t2n(gi[0]), gi_ref) <= tol_gi, (name, dl, exact_inputs)
+            assert H.rel_err(H.t2n(gw), gw_ref) <= 1e-4          # weight gradient still runs in fp32
