@@ -250,20 +250,22 @@ std::vector<torch::Tensor> conv333_backward(std::vector<APR*>& aprs, torch::Tens
             bytes = std::max<int64_t>(bytes, aprnet_conv333_tc_workspace_bytes(aprs[i]->handle(input), dl[i], (int) cin, (int) cout, (int) weights.size(0)));
         ws = torch::empty({bytes}, input.options().dtype(torch::kUInt8));
     }
+    torch::Tensor partial_tc;
+    if (tc) partial_tc = torch::empty({aprnet_conv333_tc_dw_partial_elems((int) cin, (int) cout)}, input.options());
     for (int64_t b = 0; b < input.size(0); ++b) {
         aprnet_apr* h = aprs[b]->handle(input);
+        if (tc) {
+            check(aprnet_conv333_backward_tc(h, dl[b], (int) cin, (int) cout, (int) weights.size(0), (const float*) row(input, b), n,
+                                             (const float*) row(grad_output, b), n, (const float*) weights.data_ptr(),
+                                             (float*) row(grad_input, b), (float*) grad_weights.data_ptr(), (float*) tree.data_ptr(),
+                                             (float*) grad_tree.data_ptr(), max_tree, (float*) partial_tc.data_ptr(), ws.data_ptr(), st),
+                  "conv333_backward (tensor cores)");
+            continue;
+        }
         check(aprnet_fill_tree_mean_forward(h, dl[b], dt, (int) cin, row(input, b), n, tree.data_ptr(), max_tree, st), "fill_tree_mean");
         check(aprnet_conv333_backward_weights(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(input, b), n,
                                               tree.data_ptr(), max_tree, row(grad_output, b), n, grad_weights.data_ptr(),
                                               partial.data_ptr(), st), "conv333_backward_weights");
-        if (tc) {
-            check(aprnet_conv333_backward_input_same_level_tc(h, dl[b], (int) cin, (int) cout, (int) weights.size(0), (const float*) row(grad_output, b), n,
-                                                              (const float*) weights.data_ptr(), (float*) row(grad_input, b), n, ws.data_ptr(), st),
-                  "conv333_backward_input (tensor cores)");
-            check(aprnet_conv333_backward_input_cross_level(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(grad_output, b), n,
-                                                            weights.data_ptr(), row(grad_input, b), n, grad_tree.data_ptr(), max_tree, st),
-                  "conv333_backward_input (cross-level)");
-        } else
         check(aprnet_conv333_backward_input(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(grad_output, b), n,
                                             weights.data_ptr(), row(grad_input, b), n, grad_tree.data_ptr(), max_tree, st),
               "conv333_backward_input");

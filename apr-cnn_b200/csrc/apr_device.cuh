@@ -97,3 +97,12 @@ struct AprnetProfScope {
     AprnetProfScope(const char* name, cudaStream_t st);
     ~AprnetProfScope();
 };
+
+// tensor-core helpers shared between translation units (conv333_tc.cu / conv333_tc_dw.cu)
+int* aprnet_tc_error_flag_device();
+extern "C" int aprnet_conv333_backward_weights_tc(aprnet_apr* a, int dl, int cin, int cout, int slots, const void* xrows, int xpad,
+                                                  const void* grows, int gpad, float* gw, float* partial, void* stream);
+extern "C" int64_t aprnet_conv333_tc_dw_partial_elems(int cin, int cout);
+extern "C" int aprnet_conv333_backward_input_cross_level(aprnet_apr* a, int dl, int dtype, int cin, int cout, int slots,
+                                                         const void* gout, int64_t ld_out, const void* w, void* gin,
+                                                         int64_t ld_in, void* gtree, int64_t ld_tree, void* stream);

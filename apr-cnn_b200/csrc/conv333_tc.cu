@@ -398,14 +398,57 @@ int run_pack_rows(const float* x, ll ld_x, ll n, const float* tree, ll ld_tree, 
 
 } // namespace
 
+int* aprnet_tc_error_flag_device() { return ensure_error_flag() == APRNET_OK ? g_error_flag_dev : nullptr; }
+
+int aprnet_tc_pack_rows(const float* x, ll ld_x, ll n, const float* tree, ll ld_tree, ll t, int c, int cpad, void* out, cudaStream_t st) {
+    return run_pack_rows(x, ld_x, n, tree, ld_tree, t, c, cpad, reinterpret_cast<__nv_bfloat16*>(out), st);
+}
+
+// Gather-GEMM over packed rows.  backward == 0: out[n = co] from rows of the input (k = ci);
+// backward == 1: out[n = ci] from rows of grad_output (k = co), same-level neighbours only, mirrored taps.
+int aprnet_tc_gather_conv(aprnet_apr* a, int dl, int backward, int cin, int cout, int slots, const void* rows, int kpad,
+                          ll tree_base, ll zero_row, const float* w, void* wp_ws, float* out, ll ld_out, cudaStream_t st) {
+    int rc = ensure_error_flag();
+    if (rc) return rc;
+    if (*g_error_flag_host) { aprnet_set_error("a previous tensor-core kernel gave up waiting on a barrier"); return APRNET_ERR_CUDA; }
+    const AprPlan* plan = aprnet_get_plan(a, dl, st);
+    if (!plan) return APRNET_ERR_CUDA;
+    const int k_dim = backward ? cout : cin, n_dim = backward ? cin : cout;
+    const TcGeom g = tc_geometry(1, k_dim, n_dim, slots);
+    if (g.kpad != kpad) { aprnet_set_error("packed row width %d does not match the padded channel count %d", kpad, g.kpad); return APRNET_ERR_ARG; }
+    __nv_bfloat16* wp = reinterpret_cast<__nv_bfloat16*>(wp_ws);
+    { AprnetProfScope _prof("pack_weights_bf16", st);
+    pack_weights_bf16_kernel<<<std::min(1024, aprnet_ceil_div((ll) slots * 27 * g.n_tiles * g.kpad * g.nt, 256)), 256, 0, st>>>(
+        w, slots, cin, cout, backward, n_dim, k_dim, g.nt, g.n_tiles, g.kpad, wp);
+    }
+    APRNET_LAUNCH_CHECK();
+    TcParams P;
+    P.segs = make_seg_table(aprnet_segments(a, dl, slots, false), TILE_M);
+    P.nbr = plan->nbr; P.N = plan->n; P.rows = reinterpret_cast<const __nv_bfloat16*>(rows); P.kpad = g.kpad;
+    P.tree_base = tree_base; P.zero_row = zero_row;
+    P.wp = wp; P.out = out; P.ld_out = ld_out; P.n_dim = n_dim; P.n_tiles = g.n_tiles; P.same_level_only = backward;
+    P.error_flag = g_error_flag_dev;
+    const int total = P.segs.tile_begin[P.segs.n] * g.n_tiles;
+    if (total == 0) return APRNET_OK;
+    char pname[64];
+    snprintf(pname, sizeof(pname), "%s:ci%d:co%d:dl%d", backward ? "conv333_tc_bwd_gather" : "conv333_tc_fwd", cin, cout, dl);
+    return dispatch_tc(P, g, total, st, pname);
+}
+
+size_t aprnet_tc_rows_bytes(ll rows, int channels) { return tc_geometry(rows, channels, 16, 1).rows_bytes; }
+size_t aprnet_tc_weight_bytes(int k_dim, int n_dim, int slots) { return tc_geometry(1, k_dim, n_dim, slots).w_bytes; }
+int aprnet_tc_pad(int channels) { return pad_to(channels, 16); }
+
 extern "C" int aprnet_tc_error_flag(void) { return g_error_flag_host ? *g_error_flag_host : 0; }
 
 extern "C" int64_t aprnet_conv333_tc_workspace_bytes(const aprnet_apr* a, int dl, int cin, int cout, int slots) {
     if (!a || !a->valid_dl(dl)) return -1;
-    const ll rows_f = a->number_parts(dl) + a->tree_size(dl) + 1;
-    const TcGeom f = tc_geometry(rows_f, cin, cout, slots);
-    const TcGeom b = tc_geometry(a->number_parts(dl) + 1, cout, cin, slots);
-    return (int64_t) std::max(f.rows_bytes + f.w_bytes, b.rows_bytes + b.w_bytes);
+    const ll n = a->number_parts(dl), t = a->tree_size(dl);
+    // forward: packed input rows + packed weights.  backward: packed input rows, packed dO rows,
+    // packed (transposed) weights.  One size serves both calls.
+    const size_t fwd = aprnet_tc_rows_bytes(n + t + 1, cin) + aprnet_tc_weight_bytes(cin, cout, slots);
+    const size_t bwd = aprnet_tc_rows_bytes(n + t + 1, cin) + aprnet_tc_rows_bytes(n + 1, cout) + aprnet_tc_weight_bytes(cout, cin, slots);
+    return (int64_t) std::max(fwd, bwd);
 }
 
 // forward: out = conv(in) with bf16 operands / fp32 accumulation; tree_scratch receives the fp32 tree means
@@ -415,68 +458,40 @@ extern "C" int aprnet_conv333_forward_tc(aprnet_apr* a, int dl, int cin, int cou
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && cin > 0 && cout > 0 && slots > 0 && in && w && out && tree && workspace, "bad argument");
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl) && ld_tree >= a->tree_size(dl), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
-    int rc = ensure_error_flag();
+    int rc = aprnet_fill_tree_mean_forward(a, dl, APRNET_F32, cin, in, ld_in, tree, ld_tree, st);
     if (rc) return rc;
-    if (*g_error_flag_host) { aprnet_set_error("a previous tensor-core kernel gave up waiting on a barrier"); return APRNET_ERR_CUDA; }
-    const AprPlan* plan = aprnet_get_plan(a, dl, st);
-    if (!plan) return APRNET_ERR_CUDA;
-    rc = aprnet_fill_tree_mean_forward(a, dl, APRNET_F32, cin, in, ld_in, tree, ld_tree, st);
+    const ll n = a->number_parts(dl), t = a->tree_size(dl);
+    const int kpad = aprnet_tc_pad(cin);
+    char* ws = (char*) workspace;
+    void* rows = ws;
+    void* wp = ws + aprnet_tc_rows_bytes(n + t + 1, cin);
+    rc = aprnet_tc_pack_rows(in, ld_in, n, tree, ld_tree, t, cin, kpad, rows, st);
     if (rc) return rc;
-    const ll n = plan->n, t = plan->tree_size;
-    const TcGeom g = tc_geometry(n + t + 1, cin, cout, slots);
-    __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(workspace);
-    __nv_bfloat16* wp = reinterpret_cast<__nv_bfloat16*>((char*) workspace + g.rows_bytes);
-    rc = run_pack_rows(in, ld_in, n, tree, ld_tree, t, cin, g.kpad, rows, st);
-    if (rc) return rc;
-    { AprnetProfScope _prof("pack_weights_bf16", st);
-    pack_weights_bf16_kernel<<<std::min(1024, aprnet_ceil_div((ll) slots * 27 * g.n_tiles * g.kpad * g.nt, 256)), 256, 0, st>>>(
-        w, slots, cin, cout, 0, cout, cin, g.nt, g.n_tiles, g.kpad, wp);
-    }
-    APRNET_LAUNCH_CHECK();
-    TcParams P;
-    P.segs = make_seg_table(aprnet_segments(a, dl, slots, false), TILE_M);
-    P.nbr = plan->nbr; P.N = n; P.rows = rows; P.kpad = g.kpad; P.tree_base = n; P.zero_row = n + t;
-    P.wp = wp; P.out = out; P.ld_out = ld_out; P.n_dim = cout; P.n_tiles = g.n_tiles; P.same_level_only = 0;
-    P.error_flag = g_error_flag_dev;
-    const int total = P.segs.tile_begin[P.segs.n] * g.n_tiles;
-    if (total == 0) return APRNET_OK;
-    char pname[64];
-    snprintf(pname, sizeof(pname), "conv333_tc_fwd:ci%d:co%d:dl%d", cin, cout, dl);
-    return dispatch_tc(P, g, total, st, pname);
+    return aprnet_tc_gather_conv(a, dl, 0, cin, cout, slots, rows, kpad, n, n + t, w, wp, out, ld_out, st);
 }
 
-// same-level part of the input gradient: gin[ci][q] = sum_taps sum_co W[co][ci][tap] * dO[co][mirror neighbour]
-// (written, not accumulated; the cross-level part and the tree adjoint are added by the caller afterwards)
-extern "C" int aprnet_conv333_backward_input_same_level_tc(aprnet_apr* a, int dl, int cin, int cout, int slots, const float* gout,
-                                                           int64_t ld_out, const float* w, float* gin, int64_t ld_in,
-                                                           void* workspace, void* stream) {
-    APRNET_ARG_CHECK(a && a->valid_dl(dl) && cin > 0 && cout > 0 && slots > 0 && gout && w && gin && workspace, "bad argument");
-    APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl), "leading dimension too small");
+// Complete backward pass of the 3x3x3 convolution with the contractions on the tensor cores:
+// grad_weights (accumulated into), grad_input (written; float32 (Cin, ld_in)).
+//   tree means -> packed input rows, packed dO rows -> weight gradient (tcgen05, deterministic)
+//   -> same-level input gradient (tcgen05 gather) -> cross-level part (atomicAdd) + tree adjoint.
+extern "C" int aprnet_conv333_backward_tc(aprnet_apr* a, int dl, int cin, int cout, int slots, const float* in, int64_t ld_in,
+                                          const float* gout, int64_t ld_out, const float* w, float* gin, float* gw,
+                                          float* tree, float* gtree, int64_t ld_tree, float* partial, void* workspace,
+                                          void* stream) {
+    APRNET_ARG_CHECK(a && a->valid_dl(dl) && cin > 0 && cout > 0 && slots > 0 && in && gout && w && gin && gw && tree && gtree && partial && workspace, "bad argument");
+    APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl) && ld_tree >= a->tree_size(dl), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
-    int rc = ensure_error_flag();
+    int rc = aprnet_fill_tree_mean_forward(a, dl, APRNET_F32, cin, in, ld_in, tree, ld_tree, st);
     if (rc) return rc;
-    if (*g_error_flag_host) { aprnet_set_error("a previous tensor-core kernel gave up waiting on a barrier"); return APRNET_ERR_CUDA; }
-    const AprPlan* plan = aprnet_get_plan(a, dl, st);
-    if (!plan) return APRNET_ERR_CUDA;
-    const ll n = plan->n;
-    const TcGeom g = tc_geometry(n + 1, cout, cin, slots);
-    __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(workspace);
-    __nv_bfloat16* wp = reinterpret_cast<__nv_bfloat16*>((char*) workspace + g.rows_bytes);
-    rc = run_pack_rows(gout, ld_out, n, nullptr, 0, 0, cout, g.kpad, rows, st);
-    if (rc) return rc;
-    { AprnetProfScope _prof("pack_weights_bf16", st);
-    pack_weights_bf16_kernel<<<std::min(1024, aprnet_ceil_div((ll) slots * 27 * g.n_tiles * g.kpad * g.nt, 256)), 256, 0, st>>>(
-        w, slots, cin, cout, 1, cin, cout, g.nt, g.n_tiles, g.kpad, wp);
-    }
-    APRNET_LAUNCH_CHECK();
-    TcParams P;
-    P.segs = make_seg_table(aprnet_segments(a, dl, slots, false), TILE_M);
-    P.nbr = plan->nbr; P.N = n; P.rows = rows; P.kpad = g.kpad; P.tree_base = n; P.zero_row = n;
-    P.wp = wp; P.out = gin; P.ld_out = ld_in; P.n_dim = cin; P.n_tiles = g.n_tiles; P.same_level_only = 1;
-    P.error_flag = g_error_flag_dev;
-    const int total = P.segs.tile_begin[P.segs.n] * g.n_tiles;
-    if (total == 0) return APRNET_OK;
-    char pname[64];
-    snprintf(pname, sizeof(pname), "conv333_tc_bwd_gather:ci%d:co%d:dl%d", cin, cout, dl);
-    return dispatch_tc(P, g, total, st, pname);
+    const ll n = a->number_parts(dl), t = a->tree_size(dl);
+    const int xpad = aprnet_tc_pad(cin), gpad = aprnet_tc_pad(cout);
+    char* ws = (char*) workspace;
+    void* xrows = ws;
+    void* grows = ws + aprnet_tc_rows_bytes(n + t + 1, cin);
+    void* wp = (char*) grows + aprnet_tc_rows_bytes(n + 1, cout);
+    if ((rc = aprnet_tc_pack_rows(in, ld_in, n, tree, ld_tree, t, cin, xpad, xrows, st))) return rc;
+    if ((rc = aprnet_tc_pack_rows(gout, ld_out, n, nullptr, 0, 0, cout, gpad, grows, st))) return rc;
+    if ((rc = aprnet_conv333_backward_weights_tc(a, dl, cin, cout, slots, xrows, xpad, grows, gpad, gw, partial, st))) return rc;
+    if ((rc = aprnet_tc_gather_conv(a, dl, 1, cin, cout, slots, grows, gpad, n, n, w, wp, gin, ld_in, st))) return rc;
+    return aprnet_conv333_backward_input_cross_level(a, dl, APRNET_F32, cin, cout, slots, gout, ld_out, w, gin, ld_in, gtree, ld_tree, st);
 }

@@ -342,7 +342,7 @@ def run_gpu(args):
                    "l2": "inputs larger than L2 (activations are GBs per layer)", "setup_s": t_setup, "loss": loss_val},
         "gpu_launches": launches,
         "clocks": clock_rec,
-        "kernels": {k: {"launches": v[0], "total_ms": v[1]} for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])[:12]},
+        "kernels": {k: {"launches": v[0], "total_ms": v[1]} for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])[:40]},
     }
     if e2e_ms_all:
         out["e2e"] = {"value": n_total / (e2e_ms_all / args.steps * 1e-3), "unit": "particles/s",

@@ -137,12 +137,24 @@ int64_t aprnet_conv333_tc_workspace_bytes(const aprnet_apr* apr, int level_delta
 int aprnet_conv333_forward_tc(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
                               const float* input, int64_t ld_in, const float* weights, float* output, int64_t ld_out,
                               float* tree_scratch, int64_t ld_tree, void* workspace, void* stream);
-/* Input gradient in two parts: the taps whose source is a location of the same level are a gather
- * (tensor cores; WRITES grad_input), the taps whose source is a coarser particle or a tree node are
- * scattered with atomicAdd on top and followed by the tree adjoint (CUDA cores). */
-int aprnet_conv333_backward_input_same_level_tc(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
-                                                const float* grad_output, int64_t ld_out, const float* weights,
-                                                float* grad_input, int64_t ld_in, void* workspace, void* stream);
+/* Complete backward pass with the contractions on the tensor cores.  grad_weights
+ * (num_slots, Cout, Cin, 27) is accumulated into (deterministic block partials + fixed-order second
+ * pass); grad_input (Cin, ld_in) is written.  Steps: tree means of the input -> bf16 channels-last
+ * copies of input and grad_output -> weight gradient -> same-level part of the input gradient (a
+ * gather) -> cross-level part (atomicAdd onto coarser particles / tree nodes) and tree adjoint.
+ * tree / grad_tree: (Cin, ld_tree) float scratch; partial: aprnet_conv333_tc_dw_partial_elems()
+ * floats; workspace: aprnet_conv333_tc_workspace_bytes() bytes. */
+int64_t aprnet_conv333_tc_dw_partial_elems(int cin, int cout);
+int aprnet_conv333_backward_tc(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
+                               const float* input, int64_t ld_in, const float* grad_output, int64_t ld_out,
+                               const float* weights, float* grad_input, float* grad_weights,
+                               float* tree_scratch, float* grad_tree_scratch, int64_t ld_tree,
+                               float* partial, void* workspace, void* stream);
+/* Building blocks of the above, exported for callers that keep the packed copies around. */
+int aprnet_conv333_backward_weights_tc(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
+                                       const void* packed_input_rows, int input_row_width,
+                                       const void* packed_grad_output_rows, int grad_output_row_width,
+                                       float* grad_weights, float* partial, void* stream);
 int aprnet_conv333_backward_input_cross_level(aprnet_apr* apr, int level_delta, int dtype, int cin, int cout, int num_slots,
                                               const void* grad_output, int64_t ld_out, const void* weights,
                                               void* grad_input, int64_t ld_in, void* grad_tree_scratch, int64_t ld_tree,
