@@ -500,7 +500,8 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
         .def("init_cuda", &APR::init_cuda, "copy access structures to GPU device", "with_tree"_a = true)
         .def("cuda_device_bytes", [](APR& a) { return a.dev ? aprnet_device_bytes(a.dev) : (int64_t) 0; })
         .def("plan", [](APR& a, int dl) { TORCH_CHECK(a.dev, "APR.init_cuda() must be called first");
-                                          check(aprnet_plan_build(a.dev, dl, nullptr), "plan"); }, "level_delta"_a,
+                                          check(aprnet_plan_build(a.dev, dl, nullptr), "plan");
+                                          if (g_conv_mode == 1) check(aprnet_edge_plan_build(a.dev, dl, nullptr), "edge plan"); }, "level_delta"_a,
              "Build (and cache) the neighbour table of a level delta ahead of the first convolution")
         .def("computational_ratio", &APR::computational_ratio)
         .def(py::pickle(

@@ -37,6 +37,22 @@ struct AprPlan {                 // cached per level_delta
     int32_t* nbr = nullptr;      // [27][n]
 };
 
+// Cross-level edges of one level_delta: every (output location p, tap) whose source is a coarser
+// particle or a tree node.  Edges are numbered tap-major, then by p; `src[e]` = p; the edges that end
+// at one target are listed (ascending) in tgt_edge[tgt_ptr[t] .. tgt_ptr[t+1]), targets numbered as
+// particle index, or N + tree index.
+struct EdgeGroup { long long begin, end; int tap, level; };
+struct EdgePlan {
+    long long n_edges = 0, n_targets = 0, n_active = 0;
+    int32_t* src = nullptr;        // [n_edges]
+    int32_t* tgt_ptr = nullptr;    // [n_targets + 1]
+    int32_t* tgt_edge = nullptr;   // [n_edges]
+    int32_t* active = nullptr;     // [n_active] targets with at least one edge
+    void* groups_dev = nullptr;    // device copy of the tile table (rebuilt when the slot count changes)
+    int groups_slots = -1;
+    std::vector<EdgeGroup> groups; // non-empty (tap, level) ranges in edge order
+};
+
 struct aprnet_apr {
     int device = 0;
     LevelMeta meta;
@@ -48,6 +64,7 @@ struct aprnet_apr {
     int32_t* child = nullptr;            // [8][n_tree]
     float* tree_scale = nullptr;         // [n_tree] weight of each child in its parent's mean
     std::map<int, AprPlan> plans;
+    std::map<int, EdgePlan> edge_plans;
     long long device_bytes = 0;
 
     int cml(int dl) const { return meta.level_max - dl; }
@@ -106,3 +123,18 @@ extern "C" int64_t aprnet_conv333_tc_dw_partial_elems(int cin, int cout);
 extern "C" int aprnet_conv333_backward_input_cross_level(aprnet_apr* a, int dl, int dtype, int cin, int cout, int slots,
                                                          const void* gout, int64_t ld_out, const void* w, void* gin,
                                                          int64_t ld_in, void* gtree, int64_t ld_tree, void* stream);
+
+EdgePlan* aprnet_get_edge_plan(aprnet_apr* apr, int dl, cudaStream_t stream);
+void aprnet_free_edge_plan(EdgePlan& ep);
+// edge-list GEMM: rows_out[e - e0][0..row_pad) = packed dO row src[e] times W[slot][:, :, tap]^T, for the edges of groups [g0, g1)
+int aprnet_tc_edge_gemm(aprnet_apr* a, int dl, int cin, int cout, int slots, const void* grows, int gpad, long long zero_row,
+                        const void* wp_packed, EdgePlan* ep, int g0, int g1, float* rows_out, int row_pad, cudaStream_t st);
+int aprnet_tc_pack_weights(const float* w, int slots, int cin, int cout, int mode, void* wp, cudaStream_t st);
+size_t aprnet_tc_weight_bytes(int k_dim, int n_dim, int slots);
+size_t aprnet_tc_rows_bytes(long long rows, int channels);
+int aprnet_tc_pad(int channels);
+extern "C" int64_t aprnet_edge_workspace_bytes(const aprnet_apr* a, int dl, int cin);
+extern "C" int aprnet_conv333_backward_input_cross_level_tc(aprnet_apr* a, int dl, int cin, int cout, int slots,
+                                                            const void* grows, int gpad, const float* w, float* gin,
+                                                            int64_t ld_in, float* gtree, int64_t ld_tree, void* wp_ws,
+                                                            void* edge_ws, int64_t edge_ws_bytes, void* stream);

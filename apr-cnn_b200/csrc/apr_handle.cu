@@ -291,6 +291,7 @@ extern "C" void aprnet_apr_destroy(aprnet_apr* a) {
     cudaFree(a->row_ptr); cudaFree(a->y); cudaFree(a->tree_row_ptr); cudaFree(a->tree_y);
     cudaFree(a->child); cudaFree(a->tree_scale);
     for (auto& kv : a->plans) cudaFree(kv.second.nbr);
+    for (auto& kv : a->edge_plans) aprnet_free_edge_plan(kv.second);
     delete a;
 }
 

@@ -22,6 +22,7 @@
 #include "apr_device.cuh"
 #include <cuda_bf16.h>
 #include <algorithm>
+#include <cstring>
 
 namespace {
 
@@ -153,7 +154,7 @@ __global__ void pack_rows_bf16_kernel(const float* __restrict__ x, ll ld_x, ll n
 
 // Packed weights: [slot][tap][n_tile][k chunk j][n][8] bf16 (canonical K-major operand per (slot,tap,n_tile)).
 // forward:  B[n = co][k = ci] = w[slot][co][ci][tap]
-// backward: B[n = ci][k = co] = w[slot][co][ci][26 - tap]
+// backward == 1: B[n = ci][k = co] = w[slot][co][ci][26 - tap];  backward == 2: B[n = ci][k = co] = w[slot][co][ci][tap]
 __global__ void pack_weights_bf16_kernel(const float* __restrict__ w, int slots, int cin, int cout, int backward,
                                          int n_dim, int k_dim, int nt, int n_tiles, int kpad, __nv_bfloat16* __restrict__ out) {
     const ll total = (ll) slots * 27 * n_tiles * (kpad / 8) * nt * 8;
@@ -169,7 +170,7 @@ __global__ void pack_weights_bf16_kernel(const float* __restrict__ w, int slots,
         float v = 0.f;
         if (nidx < n_dim && kidx < k_dim) {
             const int co = backward ? kidx : nidx, ci = backward ? nidx : kidx;
-            const int tp = backward ? 26 - tap : tap;
+            const int tp = (backward == 1) ? 26 - tap : tap;
             v = w[(((ll) slot * cout + co) * cin + ci) * 27 + tp];
         }
         out[e] = __float2bfloat16(v);
@@ -177,6 +178,8 @@ __global__ void pack_weights_bf16_kernel(const float* __restrict__ w, int slots,
 }
 
 // ---- main kernel -----------------------------------------------------------------------------------
+struct EdgeGroupDev { ll begin, end; int tile_begin, tap, slot, pad; };   // edges [begin, end) share one tap and one stencil slot
+
 struct TcParams {
     SegTable segs;
     const int32_t* nbr; ll N;              // neighbour table [27][N]
@@ -187,6 +190,13 @@ struct TcParams {
     int n_tiles;
     int same_level_only;                   // input-gradient mode: mask entries outside the tile's level
     int* error_flag;
+    // edge mode (cross-level part of the input gradient): one tap per tile, source rows from an edge list,
+    // result rows written channels-last as float [edge - edge_origin][row_pad]
+    int edge_mode;
+    const int32_t* edge_src;
+    const EdgeGroupDev* groups; int n_groups;
+    ll edge_origin;
+    float* out_rows; int row_pad;
 };
 
 template<int NT, int KS>
@@ -203,7 +213,6 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int kchunks = P.kpad / KS;
-    const int steps_per_tile = 27 * kchunks;
 
     if (tid == 0) {
         for (int i = 0; i <= STAGES; ++i) mbar_init(smem_u32(bars + i), 1);
@@ -215,22 +224,40 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
     tc_fence_after();
     const uint32_t tmem_d = *tmem_slot;
 
-    const int total_tiles = P.segs.tile_begin[P.segs.n] * P.n_tiles;
+    const int ntaps = P.edge_mode ? 1 : 27;
+    const int steps_per_tile = ntaps * kchunks;
+    const int total_tiles = (P.edge_mode ? P.groups[P.n_groups - 1].tile_begin +
+                                               (int) ((P.groups[P.n_groups - 1].end - P.groups[P.n_groups - 1].begin + TILE_M - 1) / TILE_M)
+                                         : P.segs.tile_begin[P.segs.n]) * P.n_tiles;
     uint32_t gstep = 0;           // stages issued so far by this block (selects buffer and mbarrier phase)
     uint32_t tiles_done = 0;
     bool failed = false;
 
     for (int work = blockIdx.x; work < total_tiles; work += gridDim.x) {
         const int tile = work / P.n_tiles, ntile = work % P.n_tiles;
-        int seg = 0;
-        while (seg + 1 < P.segs.n && tile >= P.segs.tile_begin[seg + 1]) ++seg;
-        const ll lo = P.segs.begin[seg], hi = P.segs.end[seg];
-        const ll p = lo + (ll) (tile - P.segs.tile_begin[seg]) * TILE_M + tid;
+        ll lo, hi, p;
+        int slot, tap_base;
+        if (P.edge_mode) {
+            int g0 = 0, g1 = P.n_groups - 1;              // last group whose tile_begin <= tile
+            while (g0 < g1) { const int m = (g0 + g1 + 1) >> 1; if (P.groups[m].tile_begin <= tile) g0 = m; else g1 = m - 1; }
+            lo = P.groups[g0].begin; hi = P.groups[g0].end;
+            p = lo + (ll) (tile - P.groups[g0].tile_begin) * TILE_M + tid;       // p is an edge id here
+            slot = P.groups[g0].slot; tap_base = P.groups[g0].tap;
+        } else {
+            int seg = 0;
+            while (seg + 1 < P.segs.n && tile >= P.segs.tile_begin[seg + 1]) ++seg;
+            lo = P.segs.begin[seg]; hi = P.segs.end[seg];
+            p = lo + (ll) (tile - P.segs.tile_begin[seg]) * TILE_M + tid;
+            slot = P.segs.slot[seg]; tap_base = 0;
+        }
         const bool valid = p < hi;
-        const __nv_bfloat16* wtile = P.wp + ((ll) (P.segs.slot[seg] * 27) * P.n_tiles + ntile) * ((ll) P.kpad * NT);
+        const __nv_bfloat16* wtile = P.wp + ((ll) (slot * 27 + tap_base) * P.n_tiles + ntile) * ((ll) P.kpad * NT);
         const ll w_tap_stride = (ll) P.n_tiles * P.kpad * NT;
 
         // source row of every tap for this thread's output location
+        if (P.edge_mode) {
+            idx_s[tid] = valid ? P.edge_src[p] : (int32_t) P.zero_row;
+        } else
         for (int tap = 0; tap < 27; ++tap) {
             ll r = P.zero_row;
             if (valid) {
@@ -314,7 +341,13 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
             uint32_t r[32];
             tmem_ld32(tmem_d + ((uint32_t) (warp * 32) << 16) + c0, r);
             tmem_ld_wait();
-            if (valid) {
+            if (valid && P.edge_mode) {
+                float4* dst = reinterpret_cast<float4*>(P.out_rows + (p - P.edge_origin) * P.row_pad + ntile * NT + c0);
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    if (ntile * NT + c0 + j < P.row_pad)
+                        dst[j >> 2] = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            } else if (valid) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int n = ntile * NT + c0 + j;
@@ -332,6 +365,13 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_d, NT);
+}
+
+__global__ void set_group_tile_begin_kernel(EdgeGroupDev* g, int n, int tile) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        int acc = 0;
+        for (int i = 0; i < n; ++i) { g[i].tile_begin = acc; acc += (int) ((g[i].end - g[i].begin + tile - 1) / tile); }
+    }
 }
 
 // ---- host side ----------------------------------------------------------------------------------------
@@ -428,10 +468,66 @@ int aprnet_tc_gather_conv(aprnet_apr* a, int dl, int backward, int cin, int cout
     P.tree_base = tree_base; P.zero_row = zero_row;
     P.wp = wp; P.out = out; P.ld_out = ld_out; P.n_dim = n_dim; P.n_tiles = g.n_tiles; P.same_level_only = backward;
     P.error_flag = g_error_flag_dev;
+    P.edge_mode = 0; P.edge_src = nullptr; P.groups = nullptr; P.n_groups = 0; P.edge_origin = 0; P.out_rows = nullptr; P.row_pad = 0;
     const int total = P.segs.tile_begin[P.segs.n] * g.n_tiles;
     if (total == 0) return APRNET_OK;
     char pname[64];
     snprintf(pname, sizeof(pname), "%s:ci%d:co%d:dl%d", backward ? "conv333_tc_bwd_gather" : "conv333_tc_fwd", cin, cout, dl);
+    return dispatch_tc(P, g, total, st, pname);
+}
+
+int aprnet_tc_pack_weights(const float* w, int slots, int cin, int cout, int mode, void* wp, cudaStream_t st) {
+    const int k_dim = mode ? cout : cin, n_dim = mode ? cin : cout;
+    const TcGeom g = tc_geometry(1, k_dim, n_dim, slots);
+    { AprnetProfScope _prof("pack_weights_bf16", st);
+    pack_weights_bf16_kernel<<<std::min(1024, aprnet_ceil_div((ll) slots * 27 * g.n_tiles * g.kpad * g.nt, 256)), 256, 0, st>>>(
+        w, slots, cin, cout, mode, n_dim, k_dim, g.nt, g.n_tiles, g.kpad, reinterpret_cast<__nv_bfloat16*>(wp));
+    }
+    APRNET_LAUNCH_CHECK();
+    return APRNET_OK;
+}
+
+// Edge-list GEMM for the groups [g0, g1) of an edge plan (weights already packed with mode 2).
+int aprnet_tc_edge_gemm(aprnet_apr* a, int dl, int cin, int cout, int slots, const void* grows, int gpad, ll zero_row,
+                        const void* wp_packed, EdgePlan* ep, int g0, int g1, float* rows_out, int row_pad, cudaStream_t st) {
+    int rc = ensure_error_flag();
+    if (rc) return rc;
+    if (*g_error_flag_host) { aprnet_set_error("a previous tensor-core kernel gave up waiting on a barrier"); return APRNET_ERR_CUDA; }
+    const TcGeom g = tc_geometry(1, cout, cin, slots);
+    if (g.kpad != gpad) { aprnet_set_error("packed row width %d does not match the padded channel count %d", gpad, g.kpad); return APRNET_ERR_ARG; }
+    // device tile table: one entry per group with the stencil slot of its level (depends on `slots`)
+    const int cml = a->cml(dl);
+    if (ep->groups_slots != slots) {
+        std::vector<EdgeGroupDev> tab(ep->groups.size());
+        for (size_t i = 0; i < tab.size(); ++i) {
+            tab[i].begin = ep->groups[i].begin; tab[i].end = ep->groups[i].end; tab[i].tap = ep->groups[i].tap;
+            tab[i].slot = std::min(cml - ep->groups[i].level, slots - 1); tab[i].tile_begin = 0; tab[i].pad = 0;
+        }
+        if (!ep->groups_dev) APRNET_CUDA_CHECK(cudaMalloc(&ep->groups_dev, std::max<size_t>(1, tab.size()) * sizeof(EdgeGroupDev)));
+        APRNET_CUDA_CHECK(cudaMemcpyAsync(ep->groups_dev, tab.data(), tab.size() * sizeof(EdgeGroupDev), cudaMemcpyHostToDevice, st));
+        APRNET_CUDA_CHECK(cudaStreamSynchronize(st));       // `tab` is a stack object; one-time per (plan, slot count)
+        ep->groups_slots = slots;
+    }
+    if (g1 <= g0) return APRNET_OK;
+    TcParams P;
+    memset(&P, 0, sizeof(P));
+    P.rows = reinterpret_cast<const __nv_bfloat16*>(grows); P.kpad = g.kpad; P.zero_row = zero_row; P.tree_base = zero_row;
+    P.wp = reinterpret_cast<const __nv_bfloat16*>(wp_packed); P.n_dim = cin; P.n_tiles = g.n_tiles;
+    P.error_flag = g_error_flag_dev;
+    P.edge_mode = 1; P.edge_src = ep->src; P.edge_origin = ep->groups[g0].begin; P.out_rows = rows_out; P.row_pad = row_pad;
+    // tile_begin is relative to the launch: computed in a tiny kernel-free way by launching per chunk with a
+    // host-built prefix: the table on the device holds absolute groups, so pass the sub-range and rebase.
+    P.groups = reinterpret_cast<const EdgeGroupDev*>(ep->groups_dev) + g0; P.n_groups = g1 - g0;
+    int total = 0;
+    std::vector<int> tile_begin(g1 - g0);
+    for (int i = g0; i < g1; ++i) { tile_begin[i - g0] = total; total += aprnet_ceil_div(ep->groups[i].end - ep->groups[i].begin, TILE_M); }
+    set_group_tile_begin_kernel<<<aprnet_ceil_div(g1 - g0, 128), 128, 0, st>>>(
+        reinterpret_cast<EdgeGroupDev*>(ep->groups_dev) + g0, g1 - g0, TILE_M);
+    APRNET_LAUNCH_CHECK();
+    total *= g.n_tiles;
+    if (total == 0) return APRNET_OK;
+    char pname[64];
+    snprintf(pname, sizeof(pname), "conv333_tc_edge:ci%d:co%d:dl%d", cin, cout, dl);
     return dispatch_tc(P, g, total, st, pname);
 }
 
@@ -447,7 +543,8 @@ extern "C" int64_t aprnet_conv333_tc_workspace_bytes(const aprnet_apr* a, int dl
     // forward: packed input rows + packed weights.  backward: packed input rows, packed dO rows,
     // packed (transposed) weights.  One size serves both calls.
     const size_t fwd = aprnet_tc_rows_bytes(n + t + 1, cin) + aprnet_tc_weight_bytes(cin, cout, slots);
-    const size_t bwd = aprnet_tc_rows_bytes(n + t + 1, cin) + aprnet_tc_rows_bytes(n + 1, cout) + aprnet_tc_weight_bytes(cout, cin, slots);
+    const size_t bwd = aprnet_tc_rows_bytes(n + t + 1, cin) + aprnet_tc_rows_bytes(n + 1, cout) + aprnet_tc_weight_bytes(cout, cin, slots) +
+                       (size_t) aprnet_edge_workspace_bytes(a, dl, cin);
     return (int64_t) std::max(fwd, bwd);
 }
 
@@ -493,5 +590,7 @@ extern "C" int aprnet_conv333_backward_tc(aprnet_apr* a, int dl, int cin, int co
     if ((rc = aprnet_tc_pack_rows(gout, ld_out, n, nullptr, 0, 0, cout, gpad, grows, st))) return rc;
     if ((rc = aprnet_conv333_backward_weights_tc(a, dl, cin, cout, slots, xrows, xpad, grows, gpad, gw, partial, st))) return rc;
     if ((rc = aprnet_tc_gather_conv(a, dl, 1, cin, cout, slots, grows, gpad, n, n, w, wp, gin, ld_in, st))) return rc;
-    return aprnet_conv333_backward_input_cross_level(a, dl, APRNET_F32, cin, cout, slots, gout, ld_out, w, gin, ld_in, gtree, ld_tree, st);
+    void* edge_ws = (char*) wp + aprnet_tc_weight_bytes(cout, cin, slots);
+    return aprnet_conv333_backward_input_cross_level_tc(a, dl, cin, cout, slots, grows, gpad, w, gin, ld_in, gtree, ld_tree, wp, edge_ws,
+                                                        aprnet_edge_workspace_bytes(a, dl, cin), st);
 }

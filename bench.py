@@ -341,6 +341,7 @@ def run_gpu(args):
                    "parallelism": "one APR replica per GPU, gradient all-reduce (NCCL)" if world > 1 else "single GPU",
                    "l2": "inputs larger than L2 (activations are GBs per layer)", "setup_s": t_setup, "loss": loss_val},
         "gpu_launches": launches,
+        "max_memory_gb": torch.cuda.max_memory_allocated() / 1e9, "apr_table_gb": apr.cuda_device_bytes() / 1e9,
         "clocks": clock_rec,
         "kernels": {k: {"launches": v[0], "total_ms": v[1]} for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])[:40]},
     }

@@ -159,6 +159,16 @@ int aprnet_conv333_backward_input_cross_level(aprnet_apr* apr, int level_delta, 
                                               const void* grad_output, int64_t ld_out, const void* weights,
                                               void* grad_input, int64_t ld_in, void* grad_tree_scratch, int64_t ld_tree,
                                               void* stream);
+/* Cross-level part of the input gradient without atomics: an edge-list GEMM on the tensor cores plus a
+ * per-target pull (deterministic).  The edge lists of a level delta are built once and cached
+ * (aprnet_edge_plan_build allocates; call it up front).  edge_ws: aprnet_edge_workspace_bytes() bytes. */
+int aprnet_edge_plan_build(aprnet_apr* apr, int level_delta, void* stream);
+int64_t aprnet_edge_workspace_bytes(const aprnet_apr* apr, int level_delta, int cin);
+int aprnet_conv333_backward_input_cross_level_tc(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
+                                                 const void* packed_grad_output_rows, int grad_output_row_width,
+                                                 const float* weights, float* grad_input, int64_t ld_in,
+                                                 float* grad_tree_scratch, int64_t ld_tree, void* packed_weight_ws,
+                                                 void* edge_ws, int64_t edge_ws_bytes, void* stream);
 int aprnet_tc_error_flag(void);
 
 /* ---- 1x1x1 convolution -----------------------------------------------------------------------
