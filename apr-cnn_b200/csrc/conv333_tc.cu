@@ -29,7 +29,14 @@ namespace {
 typedef long long ll;
 constexpr int MAX_SEGS = APRNET_MAX_LEVELS;
 constexpr int TILE_M = 128;
-constexpr int STAGES = 4;
+#ifndef APRNET_TC_STAGES
+#define APRNET_TC_STAGES 6
+#endif
+#ifndef APRNET_TC_AHEAD
+#define APRNET_TC_AHEAD 4
+#endif
+constexpr int STAGES = APRNET_TC_STAGES;            // shared-memory ring
+constexpr int AHEAD = APRNET_TC_AHEAD;             // stages of copies in flight; the ring slot being refilled was read by the MMAs of two steps ago
 constexpr unsigned SPIN_LIMIT = 1u << 22;
 
 struct SegTable {
@@ -54,6 +61,9 @@ inline SegTable make_seg_table(const std::vector<Segment>& segs, int tile) {
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+#ifdef APRNET_TC_DBG_NOLOAD
+    return;
+#endif
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
@@ -65,12 +75,19 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\t"
+#ifdef APRNET_TC_TESTWAIT
+                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
                  "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
                  "selp.b32 %0, 1, 0, p;\n\t}\n" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
 // bounded wait; returns false when the limit expired
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+#ifdef APRNET_TC_DBG_NOMMA
+    return true;
+#endif
     for (unsigned it = 0; it < SPIN_LIMIT; ++it)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
@@ -254,37 +271,48 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
         const __nv_bfloat16* wtile = P.wp + ((ll) (slot * 27 + tap_base) * P.n_tiles + ntile) * ((ll) P.kpad * NT);
         const ll w_tap_stride = (ll) P.n_tiles * P.kpad * NT;
 
-        // source row of every tap for this thread's output location
+        // source row of every tap for this thread's output location.  The 27 table entries are fetched
+        // as one batch of independent loads (a rolled loop with a dependent use per iteration would
+        // pay 27 DRAM round trips per tile).
         if (P.edge_mode) {
             idx_s[tid] = valid ? P.edge_src[p] : (int32_t) P.zero_row;
-        } else
-        for (int tap = 0; tap < 27; ++tap) {
-            ll r = P.zero_row;
-            if (valid) {
-                const int32_t q = P.nbr[(ll) tap * P.N + p];
-                if (P.same_level_only) { if (q >= lo && q < hi) r = q; }
-                else if (q >= 0) r = q;
-                else if (q != APRNET_NONE) r = P.tree_base + aprnet_dec_tree(q);
+        } else {
+            int32_t q[27];
+#pragma unroll
+            for (int tap = 0; tap < 27; ++tap) q[tap] = valid ? __ldg(P.nbr + (ll) tap * P.N + p) : APRNET_NONE;
+#pragma unroll
+            for (int tap = 0; tap < 27; ++tap) {
+                ll r = P.zero_row;
+                if (P.same_level_only) { if (q[tap] >= lo && q[tap] < hi) r = q[tap]; }
+                else if (q[tap] >= 0) r = q[tap];
+                else if (q[tap] != APRNET_NONE) r = P.tree_base + aprnet_dec_tree(q[tap]);
+                idx_s[tap * TILE_M + tid] = (int32_t) r;
             }
-            idx_s[tap * TILE_M + tid] = (int32_t) r;
         }
-        // (each thread only reads back its own entries: no barrier needed here)
+        __syncthreads();          // source rows are read by other threads of the block
 
         auto issue_loads = [&](int step) {
             const int tap = step / kchunks, kc = step % kchunks;
             const uint32_t buf = (gstep + (uint32_t) step) % STAGES;
             unsigned char* a_s = stage_base + buf * STAGE_BYTES;
             unsigned char* b_s = a_s + A_BYTES;
-            const __nv_bfloat16* src = P.rows + (ll) idx_s[tap * TILE_M + tid] * P.kpad + kc * KS;
+            // lanes sweep the 16-byte chunks of a row first, so one warp instruction reads whole rows
+            // (contiguous 32/64-byte pieces) instead of 32 scattered sectors
+            constexpr int CH = KS / 8, RPP = TILE_M / CH;
+            const int j = tid % CH, r0 = tid / CH;
 #pragma unroll
-            for (int j = 0; j < KS / 8; ++j) cp_async16(smem_u32(a_s + (j * TILE_M + tid) * 16), src + j * 8);
+            for (int i = 0; i < CH; ++i) {
+                const int row = i * RPP + r0;
+                const __nv_bfloat16* src = P.rows + (ll) idx_s[tap * TILE_M + row] * P.kpad + kc * KS + j * 8;
+                cp_async16(smem_u32(a_s + (j * TILE_M + row) * 16), src);
+            }
             // weights of (tap, kc): chunks j in [kc*KS/8, (kc+1)*KS/8), each NT x 16 B, contiguous in global memory
             const unsigned char* wsrc = reinterpret_cast<const unsigned char*>(wtile + (ll) tap * w_tap_stride + (ll) kc * KS * NT);
             for (int e = tid; e < B_BYTES / 16; e += TILE_M) cp_async16(smem_u32(b_s + e * 16), wsrc + e * 16);
         };
 
-        // prologue: fill STAGES-1 buffers (their previous readers, if any, must have finished)
-        for (int s = 0; s < STAGES - 1; ++s) {
+        // prologue: fill AHEAD buffers (their previous readers, if any, must have finished)
+        for (int s = 0; s < AHEAD; ++s) {
             if (s < steps_per_tile) {
                 const uint32_t g = gstep + s;
                 if (g >= STAGES) {
@@ -297,10 +325,11 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
         }
 
         for (int step = 0; step < steps_per_tile; ++step) {
-            cp_async_wait<STAGES - 2>();          // this thread's copies of `step` have landed
+            cp_async_wait<AHEAD - 1>();           // this thread's copies of `step` have landed
             fence_proxy_async();                  // make them visible to the tensor-core (async) proxy
             if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }     // uniform decision for the whole block
             const uint32_t g = gstep + step;
+#ifndef APRNET_TC_DBG_NOMMA
             if (tid == 0) {
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(stage_base + (g % STAGES) * STAGE_BYTES);
@@ -314,8 +343,9 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
                 umma_commit(smem_u32(bars + g % STAGES));
                 if (step == steps_per_tile - 1) umma_commit(smem_u32(bars + STAGES));
             }
-            // refill the buffer that the previous step's MMAs were reading
-            const int nxt = step + STAGES - 1;
+#endif
+            // refill the ring slot last read by the MMAs issued STAGES - AHEAD steps ago
+            const int nxt = step + AHEAD;
             if (nxt < steps_per_tile) {
                 const uint32_t gn = gstep + nxt;
                 if (gn >= STAGES) {
@@ -410,7 +440,7 @@ int launch_tc(const TcParams& P, int total_tiles, cudaStream_t st, const char* p
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int per_sm = std::max(1, std::min(std::min(4, 512 / NT), (int) (200 * 1024 / smem)));
+    const int per_sm = std::max(1, std::min(std::min(4, 512 / NT), (int) (225 * 1024 / (smem + 1024))));
     const int grid = std::min(total_tiles, sms * per_sm);
     { AprnetProfScope _prof(pname, st);
     kern<<<grid, TILE_M, smem, st>>>(P);

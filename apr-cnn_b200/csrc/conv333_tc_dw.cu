@@ -20,7 +20,8 @@ namespace {
 
 typedef long long ll;
 constexpr int PT = 128;            // particles per staged chunk (= threads per block)
-constexpr int XS = 3;              // ring of gathered-row stages
+constexpr int XS = 4;              // ring of gathered-row stages
+constexpr int XAHEAD = 2;          // stages of copies in flight (ring slots are refilled two MMA steps after they were read)
 constexpr unsigned SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
@@ -114,8 +115,8 @@ __global__ void __launch_bounds__(PT) conv333_tc_dw_kernel(const DwParams P) {
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* xs = smem;                                                   // XS * X_BYTES
     unsigned char* gs = xs + XS * X_BYTES;                                      // 2 * G_BYTES
-    int32_t* idx_s = reinterpret_cast<int32_t*>(gs + 2 * G_BYTES);             // [27][PT], each thread owns its column
-    uint64_t* bars = reinterpret_cast<uint64_t*>(idx_s + 27 * PT);             // XS + 1
+    int32_t* idx_s = reinterpret_cast<int32_t*>(gs + 2 * G_BYTES);             // 2 x [27][PT] source rows (by chunk parity)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(idx_s + 2 * 27 * PT);         // XS + 1
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + XS + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -137,40 +138,52 @@ __global__ void __launch_bounds__(PT) conv333_tc_dw_kernel(const DwParams P) {
 
     auto load_idx = [&](int chunk) {          // source rows of this thread's particle for all taps
         const ll p = pb + (ll) chunk * PT + tid;
-        int32_t* dst = idx_s;
+        int32_t* dst = idx_s + (chunk & 1) * 27 * PT;
+        int32_t q[27];          // one batch of independent loads, then the dependent stores
+#pragma unroll
+        for (int tap = 0; tap < 27; ++tap) q[tap] = (p < pe) ? __ldg(P.nbr + (ll) tap * P.N + p) : APRNET_NONE;
+#pragma unroll
         for (int tap = 0; tap < 27; ++tap) {
             ll r = P.zero_row;
-            if (p < pe) {
-                const int32_t q = P.nbr[(ll) tap * P.N + p];
-                if (q >= 0) r = q; else if (q != APRNET_NONE) r = P.tree_base + aprnet_dec_tree(q);
-            }
+            if (q[tap] >= 0) r = q[tap]; else if (q[tap] != APRNET_NONE) r = P.tree_base + aprnet_dec_tree(q[tap]);
             dst[tap * PT + tid] = (int32_t) r;
         }
     };
     auto issue_loads = [&](int stage) {
         const int chunk = stage / MT, mt = stage % MT;
         unsigned char* x_s = xs + (stage % XS) * X_BYTES;
-        if (mt == 0) load_idx(chunk);          // stages are issued in order, so the previous chunk's entries are no longer needed
-        const int32_t* idx = idx_s;
+        const int32_t* idx = idx_s + (chunk & 1) * 27 * PT;
+        // lanes sweep the 16-byte chunks of a row first: a warp instruction reads whole rows
+        {
+            const int j = tid % XCH, r0 = tid / XCH;
 #pragma unroll
-        for (int t = 0; t < TPM; ++t) {
-            const int tap = mt * TPM + t;
-            const ll r = tap < 27 ? (ll) idx[tap * PT + tid] : P.zero_row;
-            const __nv_bfloat16* src = P.xrows + r * P.xpad + cib * KCI;
+            for (int t = 0; t < TPM; ++t) {
+                const int tap = mt * TPM + t;
 #pragma unroll
-            for (int j = 0; j < XCH; ++j) cp_async16(smem_u32(x_s + ((t * XCH + j) * PT + tid) * 16), src + j * 8);
+                for (int i = 0; i < XCH; ++i) {
+                    const int p = i * (PT / XCH) + r0;
+                    const ll r = tap < 27 ? (ll) idx[tap * PT + p] : P.zero_row;
+                    cp_async16(smem_u32(x_s + ((t * XCH + j) * PT + p) * 16), P.xrows + r * P.xpad + cib * KCI + j * 8);
+                }
+            }
         }
         if (mt == 0) {
+            constexpr int GCH = NCO / 8;
             unsigned char* g_s = gs + (chunk & 1) * G_BYTES;
-            const ll p = pb + (ll) chunk * PT + tid;
-            const __nv_bfloat16* src = P.grows + (p < pe ? p : P.g_zero_row) * P.gpad + cob * NCO;
+            const int j = tid % GCH, r0 = tid / GCH;
 #pragma unroll
-            for (int j = 0; j < NCO / 8; ++j) cp_async16(smem_u32(g_s + (j * PT + tid) * 16), src + j * 8);
+            for (int i = 0; i < GCH; ++i) {
+                const int pl = i * (PT / GCH) + r0;
+                const ll p = pb + (ll) chunk * PT + pl;
+                cp_async16(smem_u32(g_s + (j * PT + pl) * 16), P.grows + (p < pe ? p : P.g_zero_row) * P.gpad + cob * NCO + j * 8);
+            }
         }
     };
 
     bool failed = false;
-    for (int s = 0; s < XS - 1; ++s) {
+    if (nchunks > 0) load_idx(0);
+    __syncthreads();
+    for (int s = 0; s < XAHEAD; ++s) {
         if (s < nstages) {
             issue_loads(s);
         }
@@ -178,9 +191,10 @@ __global__ void __launch_bounds__(PT) conv333_tc_dw_kernel(const DwParams P) {
     }
     for (int stage = 0; stage < nstages; ++stage) {
         const int chunk = stage / MT, mt = stage % MT;
-        cp_async_wait<XS - 2>();
+        cp_async_wait<XAHEAD - 1>();
         fence_proxy_async();
         if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }
+        if (mt == 0 && chunk + 1 < nchunks) load_idx(chunk + 1);      // read by other threads from stage (chunk, MT - XAHEAD) on, after further barriers
         if (tid == 0) {
             tc_fence_after();
             const uint32_t a_addr = smem_u32(xs + (stage % XS) * X_BYTES);
@@ -194,7 +208,7 @@ __global__ void __launch_bounds__(PT) conv333_tc_dw_kernel(const DwParams P) {
             umma_commit(smem_u32(bars + stage % XS));
             if (stage == nstages - 1) umma_commit(smem_u32(bars + XS));
         }
-        const int nxt = stage + XS - 1;
+        const int nxt = stage + XAHEAD;
         if (nxt < nstages) {
             if (nxt >= XS) {
                 const uint32_t use = nxt / XS;
@@ -259,7 +273,7 @@ template<int KCI, int NCO>
 int launch_dw(const DwParams& P, int nranges, int blocks_y, cudaStream_t st, const char* pname) {
     constexpr int MT = (27 + 128 / KCI - 1) / (128 / KCI);
     (void) MT;
-    const size_t smem = (size_t) XS * 128 * PT * 2 + 2 * (size_t) NCO * PT * 2 + 27 * PT * 4 + (XS + 1) * 8 + 16;
+    const size_t smem = (size_t) XS * 128 * PT * 2 + 2 * (size_t) NCO * PT * 2 + 2 * 27 * PT * 4 + (XS + 1) * 8 + 16;
     auto kern = conv333_tc_dw_kernel<KCI, NCO>;
     APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     dim3 grid((unsigned) nranges, (unsigned) blocks_y);

@@ -41,6 +41,7 @@ def parse_args():
     ap.add_argument("--cpu-sample", default="64,128,128", help="volume of the bounded CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layer", default="", help="cin,cout,level_delta[,ksize]: time ONE APRConv layer (forward + backward) instead of the U-Net")
     ap.add_argument("--profile-step", action="store_true",
                     help="after the timed region run one more step between cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     return ap.parse_args()
@@ -357,6 +358,75 @@ def run_gpu(args):
     return out
 
 
+
+# ---------------------------------------------------------------------------------------------
+# single-layer mode (APRConv channel sweep: configs[4] of BASELINE.json)
+# ---------------------------------------------------------------------------------------------
+def run_layer(args):
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    import pyapr
+    from pyapr.aprnet import cuda as ops
+    from _pyaprwrapper.aprnet import cuda as C
+    f = [int(v) for v in args.layer.split(",")]
+    cin, cout, dl = f[0], f[1], f[2]
+    k = f[3] if len(f) > 3 else 3
+    C.set_conv_precision("bf16" if args.dtype == "bf16" else "fp32")
+    volume = tuple(int(v) for v in args.volume.split(",")) if args.volume else (256, 512, 512)
+    blobs = blob_count(volume, args.blobs)
+    arrays, _, _ = make_inputs(volume, blobs, 3000, dev)
+    apr = pyapr.apr_from_arrays(arrays, "layer")
+    apr.init_cuda()
+    apr.plan(dl)
+    n = int(pyapr.aprnet.utils.number_particles(apr, dl))
+    cml = arrays.level_max - dl
+    t = int(arrays.tree_row_ptr[sum(arrays.dims[l][0] * arrays.dims[l][1] for l in range(0, cml))])
+    torch.manual_seed(7)
+    conv = ops.APRConv(cin, cout, nstencils=2, kernel_size=(k, k, k), bias=False).to(dev)
+    x = torch.rand(1, cin, n, device=dev, requires_grad=True)
+    go = torch.randn(1, cout, n, device=dev)
+    ld = torch.full((1,), dl, dtype=torch.int32)
+
+    def step():
+        x.grad = None
+        conv.weight.grad = None
+        conv(x, [apr], ld).backward(go)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    C.profile_read()
+    C.profile_enable(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    C.profile_enable(False)
+    prof = C.profile_read()
+    if args.profile_step:
+        torch.cuda.profiler.start()
+        step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    peaks = load_peaks()
+    flops = (54.0 if k == 3 else 2.0) * cin * cout * n
+    byts = (4.0 * cin + 4.0 * cout + 2.0) * n + (8.0 * cin * t if k == 3 else 0.0)
+    out = {"metric": "APRConv layer fwd+bwd particles/s", "value": n / (ms * 1e-3), "unit": "particles/s", "n_gpus": 1,
+           "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "dtype": args.dtype,
+           "data": "synthetic",
+           "config": {"workload": "APRConv %dx%dx%d %d->%d at level_delta %d, forward + backward, %dx%dx%d volume" % (k, k, k, cin, cout, dl, *volume),
+                      "particles": n, "tree_nodes": t},
+           "algorithmic": {"flops_per_pass": flops, "bytes_per_pass": byts,
+                           "tensor_roofline_ms_per_pass": flops / (peaks["tflops"] * 1e12) * 1e3,
+                           "hbm_roofline_ms_per_pass": byts / (peaks["hbm_gbs"] * 1e9) * 1e3},
+           "kernels": {kk: {"launches": v[0] / args.steps, "ms": v[1] / args.steps} for kk, v in sorted(prof.items(), key=lambda kv: -kv[1][1])}}
+    return out
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -372,7 +442,7 @@ def main():
                "e2e": {"value": cb["value"], "unit": "particles/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(out))
         return
-    out = run_gpu(args)
+    out = run_layer(args) if args.layer else run_gpu(args)
     if out is not None:
         print(json.dumps(out))
 
