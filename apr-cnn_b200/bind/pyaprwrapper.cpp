@@ -180,7 +180,7 @@ inline void zero_padding(torch::Tensor& t, int64_t b, int64_t valid) {
 }
 
 // ---- 3x3x3 convolution ------------------------------------------------------------------------
-torch::Tensor conv333_forward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights, torch::Tensor level_delta) {
+static std::vector<torch::Tensor> conv333_forward_impl(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights, torch::Tensor level_delta, bool keep_tree) {
     CHECK_INPUT(input); CHECK_INPUT(weights);
     check_batch(aprs, input);
     TORCH_CHECK(weights.dim() == 6 && weights.size(3) == 3 && weights.size(4) == 3 && weights.size(5) == 3, "weights must be (levels, Cout, Cin, 3, 3, 3)");
@@ -196,17 +196,19 @@ torch::Tensor conv333_forward(std::vector<APR*>& aprs, torch::Tensor input, torc
     }
     const int64_t cin = input.size(1), cout = weights.size(1), n = input.size(2);
     auto output = torch::empty({input.size(0), cout, n}, input.options());
-    auto tree = torch::empty({cin, max_tree}, input.options());
+    // one tree buffer per batch item when the caller keeps it for the backward pass, else one shared scratch
+    auto tree_all = torch::empty({keep_tree ? input.size(0) : 1, cin, max_tree}, input.options());
     const int dt = dtype_id(input);
     const bool tc = g_conv_mode == 1 && dt == APRNET_F32;
     torch::Tensor ws;
     if (tc) {
         int64_t bytes = 256;
         for (size_t i = 0; i < aprs.size(); ++i)
-            bytes = std::max<int64_t>(bytes, aprnet_conv333_tc_workspace_bytes(aprs[i]->handle(input), dl[i], (int) cin, (int) cout, (int) weights.size(0)));
+            bytes = std::max<int64_t>(bytes, aprnet_conv333_tc_forward_workspace_bytes(aprs[i]->handle(input), dl[i], (int) cin, (int) cout, (int) weights.size(0)));
         ws = torch::empty({bytes}, input.options().dtype(torch::kUInt8));
     }
     for (int64_t b = 0; b < input.size(0); ++b) {
+        auto tree = tree_all.select(0, keep_tree ? b : 0);
         if (tc)
             check(aprnet_conv333_forward_tc(aprs[b]->handle(input), dl[b], (int) cin, (int) cout, (int) weights.size(0), (const float*) row(input, b), n,
                                             (const float*) weights.data_ptr(), (float*) row(output, b), n, (float*) tree.data_ptr(), max_tree,
@@ -217,11 +219,20 @@ torch::Tensor conv333_forward(std::vector<APR*>& aprs, torch::Tensor input, torc
                   "conv333_forward");
         zero_padding(output, b, aprs[b]->number_parts(dl[b]));
     }
-    return output;
+    return {output, tree_all};
 }
 
-std::vector<torch::Tensor> conv333_backward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights,
-                                            torch::Tensor grad_output, torch::Tensor level_delta) {
+torch::Tensor conv333_forward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights, torch::Tensor level_delta) {
+    return conv333_forward_impl(aprs, input, weights, level_delta, false)[0];
+}
+
+// same, but also returns the tree means (B, Cin, T) so that the backward pass need not recompute them
+std::vector<torch::Tensor> conv333_forward_keep_tree(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights, torch::Tensor level_delta) {
+    return conv333_forward_impl(aprs, input, weights, level_delta, true);
+}
+
+static std::vector<torch::Tensor> conv333_backward_impl(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights,
+                                            torch::Tensor grad_output, torch::Tensor level_delta, c10::optional<torch::Tensor> saved_tree) {
     CHECK_INPUT(input); CHECK_INPUT(weights); CHECK_INPUT(grad_output);
     check_batch(aprs, input);
     TORCH_CHECK(grad_output.dim() == 3 && grad_output.size(0) == input.size(0) && grad_output.size(1) == weights.size(1) &&
@@ -235,14 +246,19 @@ std::vector<torch::Tensor> conv333_backward(std::vector<APR*>& aprs, torch::Tens
         max_tree = std::max<int64_t>(max_tree, aprnet_tree_size(aprs[i]->handle(input), dl[i]));
     }
     const int64_t cin = input.size(1), cout = weights.size(1), n = input.size(2);
-    auto tree = torch::empty({cin, max_tree}, input.options());
-    auto grad_tree = torch::empty({cin, max_tree}, input.options());
-    auto grad_input = torch::zeros_like(input);
-    auto grad_weights = torch::zeros_like(weights);
-    auto partial = torch::empty({aprnet_conv333_partial_elems((int) cin, (int) cout)}, input.options());
     const int dt = dtype_id(input);
     void* st = stream_of(input);
     const bool tc = g_conv_mode == 1 && dt == APRNET_F32;
+    const bool have_tree = saved_tree.has_value() && saved_tree->defined() && saved_tree->dim() == 3 && saved_tree->size(0) == input.size(0) &&
+                           saved_tree->size(1) == cin && saved_tree->size(2) == max_tree && saved_tree->is_contiguous() &&
+                           saved_tree->scalar_type() == input.scalar_type();
+    auto tree_all = have_tree ? *saved_tree : torch::empty({1, cin, max_tree}, input.options());
+    auto grad_tree = torch::empty({cin, max_tree}, input.options());
+    // the tensor-core path writes every valid entry of grad_input; the CUDA-core path accumulates into zeros
+    auto grad_input = tc ? torch::empty_like(input) : torch::zeros_like(input);
+    auto grad_weights = torch::zeros_like(weights);
+    torch::Tensor partial;
+    if (!tc) partial = torch::empty({aprnet_conv333_partial_elems((int) cin, (int) cout)}, input.options());
     torch::Tensor ws;
     if (tc) {
         int64_t bytes = 256;
@@ -254,14 +270,18 @@ std::vector<torch::Tensor> conv333_backward(std::vector<APR*>& aprs, torch::Tens
     if (tc) partial_tc = torch::empty({aprnet_conv333_tc_dw_partial_elems((int) cin, (int) cout)}, input.options());
     for (int64_t b = 0; b < input.size(0); ++b) {
         aprnet_apr* h = aprs[b]->handle(input);
+        auto tree = tree_all.select(0, have_tree ? b : 0);
         if (tc) {
             check(aprnet_conv333_backward_tc(h, dl[b], (int) cin, (int) cout, (int) weights.size(0), (const float*) row(input, b), n,
                                              (const float*) row(grad_output, b), n, (const float*) weights.data_ptr(),
                                              (float*) row(grad_input, b), (float*) grad_weights.data_ptr(), (float*) tree.data_ptr(),
-                                             (float*) grad_tree.data_ptr(), max_tree, (float*) partial_tc.data_ptr(), ws.data_ptr(), st),
+                                             have_tree ? 1 : 0, (float*) grad_tree.data_ptr(), max_tree, (float*) partial_tc.data_ptr(),
+                                             ws.data_ptr(), st),
                   "conv333_backward (tensor cores)");
+            zero_padding(grad_input, b, aprs[b]->number_parts(dl[b]));
             continue;
         }
+        if (!have_tree)
         check(aprnet_fill_tree_mean_forward(h, dl[b], dt, (int) cin, row(input, b), n, tree.data_ptr(), max_tree, st), "fill_tree_mean");
         check(aprnet_conv333_backward_weights(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(input, b), n,
                                               tree.data_ptr(), max_tree, row(grad_output, b), n, grad_weights.data_ptr(),
@@ -271,6 +291,16 @@ std::vector<torch::Tensor> conv333_backward(std::vector<APR*>& aprs, torch::Tens
               "conv333_backward_input");
     }
     return {grad_input, grad_weights};
+}
+
+std::vector<torch::Tensor> conv333_backward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights,
+                                            torch::Tensor grad_output, torch::Tensor level_delta) {
+    return conv333_backward_impl(aprs, input, weights, grad_output, level_delta, c10::nullopt);
+}
+
+std::vector<torch::Tensor> conv333_backward_with_tree(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights,
+                                                      torch::Tensor grad_output, torch::Tensor level_delta, torch::Tensor tree) {
+    return conv333_backward_impl(aprs, input, weights, grad_output, level_delta, tree);
 }
 
 // ---- 1x1x1 convolution ------------------------------------------------------------------------
@@ -534,6 +564,9 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
     cuda.def("conv111_backward", &conv111_backward, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a);
     cuda.def("conv333_forward", &conv333_forward, "aprs"_a, "input"_a, "weights"_a, "level_delta"_a);
     cuda.def("conv333_backward", &conv333_backward, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a);
+    // extensions: keep the tree means of the forward pass for the backward pass
+    cuda.def("conv333_forward_keep_tree", &conv333_forward_keep_tree, "aprs"_a, "input"_a, "weights"_a, "level_delta"_a);
+    cuda.def("conv333_backward_with_tree", &conv333_backward_with_tree, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a, "tree"_a);
     cuda.def("upsample_const_forward", &upsample_const_forward, "aprs"_a, "input"_a, "level_delta"_a);
     cuda.def("upsample_const_backward", &upsample_const_backward, "aprs"_a, "grad_output"_a, "level_delta"_a);
     cuda.def("restrict_kernel333_forward", &restrict_kernel_333_forward, "weights"_a, "num_levels"_a);

@@ -139,32 +139,39 @@ __host__ __device__ constexpr uint32_t make_idesc(int n) {
 
 // ---- operand packing --------------------------------------------------------------------------------
 // rows [0, n): x[:, p]; rows [n, n + t): tree[:, p - n]; row n + t: zeros.  Channels padded to cpad.
-__global__ void pack_rows_bf16_kernel(const float* __restrict__ x, ll ld_x, ll n, const float* __restrict__ tree, ll ld_tree, ll t,
-                                      int c, int cpad, __nv_bfloat16* __restrict__ out) {
-    __shared__ float tile[32][33];
-    const ll r0 = (ll) blockIdx.x * 32;
+__global__ void __launch_bounds__(256) pack_rows_bf16_kernel(const float* __restrict__ x, ll ld_x, ll n, const float* __restrict__ tree, ll ld_tree, ll t,
+                                                             int c, int cpad, __nv_bfloat16* __restrict__ out) {
+    // tile: 32 channels x 128 rows.  Reads are coalesced along the row (particle) axis of the channel-major
+    // source, writes are 16-byte pieces (8 channels) of the packed rows.
+    __shared__ float tile[32][129];
+    const ll r0 = (ll) blockIdx.x * 128;
     const int c0 = blockIdx.y * 32;
     const ll rows = n + t + 1;
-    {   // coalesced read along the row (particle) axis
-        const int cl = threadIdx.y;      // 0..7 -> 4 passes
-        for (int cc = cl; cc < 32; cc += 8) {
-            const ll r = r0 + threadIdx.x;
-            const int ch = c0 + cc;
-            float v = 0.f;
-            if (ch < c && r < n + t) v = (r < n) ? x[(ll) ch * ld_x + r] : tree[(ll) ch * ld_tree + (r - n)];
-            tile[cc][threadIdx.x] = v;
+    const int lane = threadIdx.x & 31, wrp = threadIdx.x >> 5;      // 8 warps
+#pragma unroll
+    for (int cc = wrp; cc < 32; cc += 8) {
+        const int ch = c0 + cc;
+        float v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const ll r = r0 + lane + 32 * k;
+            v[k] = 0.f;
+            if (ch < c && r < n + t) v[k] = (r < n) ? x[(ll) ch * ld_x + r] : tree[(ll) ch * ld_tree + (r - n)];
         }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tile[cc][lane + 32 * k] = v[k];
     }
     __syncthreads();
-    {   // write: thread -> (row, pair of channels), rows of the packed matrix are contiguous
-        const int tid = threadIdx.y * 32 + threadIdx.x;          // 256 threads
-        for (int e = tid; e < 32 * 16; e += 256) {
-            const int rr = e >> 4, cp = (e & 15) * 2;
-            const ll r = r0 + rr;
-            if (r < rows && c0 + cp < cpad) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(tile[cp][rr], tile[cp + 1][rr]);
-                *reinterpret_cast<__nv_bfloat162*>(out + r * cpad + c0 + cp) = v;
-            }
+    // 128 rows x 4 pieces of 8 channels; consecutive threads take consecutive pieces of a row
+#pragma unroll
+    for (int e = threadIdx.x; e < 128 * 4; e += 256) {
+        const int rr = e >> 2, piece = e & 3;
+        const ll r = r0 + rr;
+        if (r < rows && c0 + piece * 8 < cpad) {
+            __nv_bfloat162 h[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(tile[piece * 8 + 2 * i][rr], tile[piece * 8 + 2 * i + 1][rr]);
+            *reinterpret_cast<uint4*>(out + r * cpad + c0 + piece * 8) = *reinterpret_cast<uint4*>(h);
         }
     }
 }
@@ -458,9 +465,9 @@ int dispatch_tc(const TcParams& P, const TcGeom& g, int total_tiles, cudaStream_
 }
 
 int run_pack_rows(const float* x, ll ld_x, ll n, const float* tree, ll ld_tree, ll t, int c, int cpad, __nv_bfloat16* out, cudaStream_t st) {
-    dim3 grid((unsigned) aprnet_ceil_div(n + t + 1, 32), (unsigned) aprnet_ceil_div(cpad, 32));
+    dim3 grid((unsigned) aprnet_ceil_div(n + t + 1, 128), (unsigned) aprnet_ceil_div(cpad, 32));
     { AprnetProfScope _prof("pack_rows_bf16", st);
-    pack_rows_bf16_kernel<<<grid, dim3(32, 8), 0, st>>>(x, ld_x, n, tree, ld_tree, t, c, cpad, out);
+    pack_rows_bf16_kernel<<<grid, 256, 0, st>>>(x, ld_x, n, tree, ld_tree, t, c, cpad, out);
     }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
@@ -578,6 +585,11 @@ extern "C" int64_t aprnet_conv333_tc_workspace_bytes(const aprnet_apr* a, int dl
     return (int64_t) std::max(fwd, bwd);
 }
 
+extern "C" int64_t aprnet_conv333_tc_forward_workspace_bytes(const aprnet_apr* a, int dl, int cin, int cout, int slots) {
+    if (!a || !a->valid_dl(dl)) return -1;
+    return (int64_t) (aprnet_tc_rows_bytes(a->number_parts(dl) + a->tree_size(dl) + 1, cin) + aprnet_tc_weight_bytes(cin, cout, slots));
+}
+
 // forward: out = conv(in) with bf16 operands / fp32 accumulation; tree_scratch receives the fp32 tree means
 extern "C" int aprnet_conv333_forward_tc(aprnet_apr* a, int dl, int cin, int cout, int slots, const float* in, int64_t ld_in,
                                          const float* w, float* out, int64_t ld_out, float* tree, int64_t ld_tree,
@@ -603,12 +615,12 @@ extern "C" int aprnet_conv333_forward_tc(aprnet_apr* a, int dl, int cin, int cou
 //   -> same-level input gradient (tcgen05 gather) -> cross-level part (atomicAdd) + tree adjoint.
 extern "C" int aprnet_conv333_backward_tc(aprnet_apr* a, int dl, int cin, int cout, int slots, const float* in, int64_t ld_in,
                                           const float* gout, int64_t ld_out, const float* w, float* gin, float* gw,
-                                          float* tree, float* gtree, int64_t ld_tree, float* partial, void* workspace,
-                                          void* stream) {
+                                          float* tree, int tree_valid, float* gtree, int64_t ld_tree, float* partial,
+                                          void* workspace, void* stream) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && cin > 0 && cout > 0 && slots > 0 && in && gout && w && gin && gw && tree && gtree && partial && workspace, "bad argument");
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl) && ld_tree >= a->tree_size(dl), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
-    int rc = aprnet_fill_tree_mean_forward(a, dl, APRNET_F32, cin, in, ld_in, tree, ld_tree, st);
+    int rc = tree_valid ? APRNET_OK : aprnet_fill_tree_mean_forward(a, dl, APRNET_F32, cin, in, ld_in, tree, ld_tree, st);
     if (rc) return rc;
     const ll n = a->number_parts(dl), t = a->tree_size(dl);
     const int xpad = aprnet_tc_pad(cin), gpad = aprnet_tc_pad(cout);

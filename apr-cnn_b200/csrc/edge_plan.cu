@@ -217,7 +217,7 @@ extern "C" int aprnet_edge_plan_build(aprnet_apr* a, int dl, void* stream) {
 
 extern "C" int64_t aprnet_edge_workspace_bytes(const aprnet_apr* a, int dl, int cin) {
     if (!a || !a->valid_dl(dl)) return -1;
-    const ll cap = 1ll << 30;
+    const ll cap = 8ll << 30;     // bounds the edge-row workspace; larger = fewer pull passes over the target list
     const ll all = 27 * a->number_parts(dl) * (ll) aprnet_tc_pad(cin) * 4;
     return (int64_t) std::max<ll>(256, std::min(cap, all));
 }

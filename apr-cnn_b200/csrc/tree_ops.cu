@@ -18,29 +18,43 @@ template<typename T> struct DT;
 template<> struct DT<float> { static constexpr int id = APRNET_F32; };
 template<> struct DT<double> { static constexpr int id = APRNET_F64; };
 
-// parent level lp: tree[t] = scale[t] * sum(children)
+// parent level lp: tree[t] = scale[t] * sum(children).  All child values of the block's channels are
+// requested before any is used (CH_PER_BLOCK x 8 independent loads in flight per thread).
 template<typename T>
 __global__ void tree_mean_level_kernel(const int32_t* __restrict__ child, const float* __restrict__ scale, ll n_tree,
                                        ll tb, ll te, const T* __restrict__ in, ll ld_in, T* __restrict__ tree,
                                        ll ld_tree, int C, ll up_off, int use_up) {
     const ll t = tb + (ll) blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= te) return;
-    int32_t ch[8];
+    // resolve the eight child slots to (pointer base, offset) once
+    ll off[8];
+    bool from_tree[8], present[8], coded[8];
 #pragma unroll
-    for (int s = 0; s < 8; ++s) ch[s] = child[(ll) s * n_tree + t];
+    for (int s = 0; s < 8; ++s) {
+        const int32_t v = child[(ll) s * n_tree + t];
+        present[s] = v != APRNET_NONE;
+        coded[s] = v < APRNET_NONE;
+        from_tree[s] = v < APRNET_NONE && !use_up;
+        off[s] = v >= 0 ? (ll) v : (v == APRNET_NONE ? 0 : aprnet_dec_tree(v) + (use_up ? up_off : 0));
+    }
     const T f = (T) scale[t];
-    const int c0 = blockIdx.y * CH_PER_BLOCK, c1 = min(C, c0 + CH_PER_BLOCK);
-    for (int c = c0; c < c1; ++c) {
+    const int c0 = blockIdx.y * CH_PER_BLOCK;
+    T vals[CH_PER_BLOCK][8];
+#pragma unroll
+    for (int k = 0; k < CH_PER_BLOCK; ++k) {
+        const int c = min(c0 + k, C - 1);
         const T* x = in + (ll) c * ld_in;
         const T* tr = tree + (ll) c * ld_tree;
-        T s_part = 0, s_tree = 0;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            const int32_t v = ch[s];
-            if (v >= 0) s_part += x[v];
-            else if (v != APRNET_NONE) s_tree += use_up ? x[aprnet_dec_tree(v) + up_off] : tr[aprnet_dec_tree(v)];
-        }
-        tree[(ll) c * ld_tree + t] = f * (s_part + s_tree);
+        for (int s = 0; s < 8; ++s) vals[k][s] = present[s] ? (from_tree[s] ? tr[off[s]] : x[off[s]]) : T(0);
+    }
+#pragma unroll
+    for (int k = 0; k < CH_PER_BLOCK; ++k) {
+        if (c0 + k >= C) break;
+        T s_part = 0, s_tree = 0;       // particles first, then tree children (fixed order)
+#pragma unroll
+        for (int s = 0; s < 8; ++s) { if (coded[s]) s_tree += vals[k][s]; else s_part += vals[k][s]; }
+        tree[(ll) (c0 + k) * ld_tree + t] = f * (s_part + s_tree);
     }
 }
 
@@ -51,20 +65,36 @@ __global__ void tree_mean_level_backward_kernel(const int32_t* __restrict__ chil
                                                 T* __restrict__ gtree, ll ld_tree, int C, ll up_off, int use_up) {
     const ll t = tb + (ll) blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= te) return;
-    int32_t ch[8];
+    ll off[8];
+    bool to_tree[8], present[8];
 #pragma unroll
-    for (int s = 0; s < 8; ++s) ch[s] = child[(ll) s * n_tree + t];
+    for (int s = 0; s < 8; ++s) {
+        const int32_t v = child[(ll) s * n_tree + t];
+        present[s] = v != APRNET_NONE;
+        to_tree[s] = v < APRNET_NONE && !use_up;
+        off[s] = v >= 0 ? (ll) v : (v == APRNET_NONE ? 0 : aprnet_dec_tree(v) + (use_up ? up_off : 0));
+    }
     const T f = (T) scale[t];
-    const int c0 = blockIdx.y * CH_PER_BLOCK, c1 = min(C, c0 + CH_PER_BLOCK);
-    for (int c = c0; c < c1; ++c) {
-        T* g = gin + (ll) c * ld_in;
-        T* gt = gtree + (ll) c * ld_tree;
-        const T v = f * gt[t];
+    const int c0 = blockIdx.y * CH_PER_BLOCK;
+    T g[CH_PER_BLOCK];
+#pragma unroll
+    for (int k = 0; k < CH_PER_BLOCK; ++k) g[k] = f * gtree[(ll) min(c0 + k, C - 1) * ld_tree + t];
+    T old[CH_PER_BLOCK][8];
+#pragma unroll
+    for (int k = 0; k < CH_PER_BLOCK; ++k) {
+        const int c = min(c0 + k, C - 1);
+#pragma unroll
+        for (int s = 0; s < 8; ++s) old[k][s] = present[s] ? (to_tree[s] ? gtree[(ll) c * ld_tree + off[s]] : gin[(ll) c * ld_in + off[s]]) : T(0);
+    }
+#pragma unroll
+    for (int k = 0; k < CH_PER_BLOCK; ++k) {
+        if (c0 + k >= C) break;
+        const int c = c0 + k;
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
-            const int32_t q = ch[s];
-            if (q >= 0) g[q] += v;
-            else if (q != APRNET_NONE) { if (use_up) g[aprnet_dec_tree(q) + up_off] += v; else gt[aprnet_dec_tree(q)] += v; }
+            if (!present[s]) continue;
+            if (to_tree[s]) gtree[(ll) c * ld_tree + off[s]] = old[k][s] + g[k];
+            else gin[(ll) c * ld_in + off[s]] = old[k][s] + g[k];
         }
     }
 }

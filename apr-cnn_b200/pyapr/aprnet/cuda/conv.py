@@ -12,7 +12,7 @@ from torch.autograd import Function
 from torch.nn import init
 
 from _pyaprwrapper.data_containers import APRPtrVector
-from _pyaprwrapper.aprnet.cuda import (conv111_backward, conv111_forward, conv333_backward, conv333_forward,
+from _pyaprwrapper.aprnet.cuda import (conv111_backward, conv111_forward, conv333_backward_with_tree, conv333_forward_keep_tree,
                                        restrict_kernel333_backward, restrict_kernel333_forward)
 
 
@@ -25,17 +25,19 @@ class Conv333Function(Function):
         expanded = restrict_kernel333_forward(weights, num_levels)
         ctx.aprs = aprs
         ctx.num_stencils = weights.shape[0]
-        ctx.save_for_backward(inputs, expanded, bias, level_deltas.clone())
-        out = conv333_forward(APRPtrVector(aprs), inputs, expanded, level_deltas)
+        # the tree means computed by the forward pass are kept (1/7 of the input's size) so that the
+        # backward pass does not have to fill the tree again
+        out, tree = conv333_forward_keep_tree(APRPtrVector(aprs), inputs, expanded, level_deltas)
+        ctx.save_for_backward(inputs, expanded, bias, level_deltas.clone(), tree)
         if bias is not None:
             out = out + bias.view(1, -1, 1)
         return out
 
     @staticmethod
     def backward(ctx, grad_output):
-        inputs, expanded, bias, level_deltas = ctx.saved_tensors
+        inputs, expanded, bias, level_deltas, tree = ctx.saved_tensors
         grad_output = grad_output.contiguous()
-        grad_input, grad_expanded = conv333_backward(APRPtrVector(ctx.aprs), inputs, expanded, grad_output, level_deltas)
+        grad_input, grad_expanded = conv333_backward_with_tree(APRPtrVector(ctx.aprs), inputs, expanded, grad_output, level_deltas, tree)
         grad_weights = restrict_kernel333_backward(grad_expanded, ctx.num_stencils)
         grad_bias = grad_output.sum(dim=(0, 2)) if bias is not None else None
         return grad_input, grad_weights, grad_bias, None, None

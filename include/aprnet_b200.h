@@ -133,7 +133,8 @@ int aprnet_conv333_backward_weights(aprnet_apr* apr, int level_delta, int dtype,
  * weights (relative error <= 2e-2).  `workspace` needs aprnet_conv333_tc_workspace_bytes() bytes,
  * 256-byte aligned.  Waits inside the kernels are bounded; aprnet_tc_error_flag() becomes non-zero
  * if one ever expired, and later calls then fail with APRNET_ERR_CUDA. */
-int64_t aprnet_conv333_tc_workspace_bytes(const aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots);
+int64_t aprnet_conv333_tc_workspace_bytes(const aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots);          /* backward (and forward) */
+int64_t aprnet_conv333_tc_forward_workspace_bytes(const aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots);  /* forward only */
 int aprnet_conv333_forward_tc(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
                               const float* input, int64_t ld_in, const float* weights, float* output, int64_t ld_out,
                               float* tree_scratch, int64_t ld_tree, void* workspace, void* stream);
@@ -142,13 +143,14 @@ int aprnet_conv333_forward_tc(aprnet_apr* apr, int level_delta, int cin, int cou
  * pass); grad_input (Cin, ld_in) is written.  Steps: tree means of the input -> bf16 channels-last
  * copies of input and grad_output -> weight gradient -> same-level part of the input gradient (a
  * gather) -> cross-level part (atomicAdd onto coarser particles / tree nodes) and tree adjoint.
- * tree / grad_tree: (Cin, ld_tree) float scratch; partial: aprnet_conv333_tc_dw_partial_elems()
+ * tree / grad_tree: (Cin, ld_tree) float scratch (pass tree_scratch_is_valid = 1 when tree_scratch still
+ * holds the tree means that the forward call left there: the fill is then skipped); partial: aprnet_conv333_tc_dw_partial_elems()
  * floats; workspace: aprnet_conv333_tc_workspace_bytes() bytes. */
 int64_t aprnet_conv333_tc_dw_partial_elems(int cin, int cout);
 int aprnet_conv333_backward_tc(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
                                const float* input, int64_t ld_in, const float* grad_output, int64_t ld_out,
                                const float* weights, float* grad_input, float* grad_weights,
-                               float* tree_scratch, float* grad_tree_scratch, int64_t ld_tree,
+                               float* tree_scratch, int tree_scratch_is_valid, float* grad_tree_scratch, int64_t ld_tree,
                                float* partial, void* workspace, void* stream);
 /* Building blocks of the above, exported for callers that keep the packed copies around. */
 int aprnet_conv333_backward_weights_tc(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
