@@ -17,21 +17,29 @@ from torch import nn
 
 
 class ConvNormAct(nn.Module):
-    def __init__(self, ops, cin, cout, nstencils, kernel_size, num_groups):
+    """conv -> GroupNorm -> ReLU.  When the operator namespace offers a fused `GroupNormReLU` (same
+    function and parameters as nn.GroupNorm followed by nn.ReLU) and `fused_norm` is set, it is used."""
+
+    def __init__(self, ops, cin, cout, nstencils, kernel_size, num_groups, fused_norm=True):
         super().__init__()
         self.conv = ops.APRConv(cin, cout, nstencils=nstencils, kernel_size=kernel_size, bias=False)
-        self.norm = nn.GroupNorm(min(num_groups, cout) if num_groups else cout, cout)
-        self.act = nn.ReLU()
+        groups = min(num_groups, cout) if num_groups else cout
+        if fused_norm and hasattr(ops, "GroupNormReLU"):
+            self.norm = ops.GroupNormReLU(groups, cout)
+            self.act = nn.Identity()
+        else:
+            self.norm = nn.GroupNorm(groups, cout)
+            self.act = nn.ReLU()
 
     def forward(self, x, aprs, level_deltas):
         return self.act(self.norm(self.conv(x, aprs, level_deltas)))
 
 
 class Stage(nn.Module):
-    def __init__(self, ops, cin, cout, nstencils, n_conv, num_groups):
+    def __init__(self, ops, cin, cout, nstencils, n_conv, num_groups, fused_norm=True):
         super().__init__()
         widths = [cin] + [cout] * n_conv
-        self.blocks = nn.ModuleList(ConvNormAct(ops, widths[i], widths[i + 1], nstencils, (3, 3, 3), num_groups)
+        self.blocks = nn.ModuleList(ConvNormAct(ops, widths[i], widths[i + 1], nstencils, (3, 3, 3), num_groups, fused_norm)
                                     for i in range(n_conv))
 
     def forward(self, x, aprs, level_deltas):
@@ -41,23 +49,23 @@ class Stage(nn.Module):
 
 
 class APRUNet(nn.Module):
-    def __init__(self, ops, in_channels, out_channels, depth=3, n_filters_base=32, n_conv_per_block=2, n_stencils=2):
+    def __init__(self, ops, in_channels, out_channels, depth=3, n_filters_base=32, n_conv_per_block=2, n_stencils=2, fused_norm=True):
         super().__init__()
         widths = [n_filters_base * 2 ** i for i in range(depth + 1)]
         groups = n_filters_base
         self.depth = depth
-        self.enc = nn.ModuleList([Stage(ops, in_channels, widths[0], n_stencils, n_conv_per_block, groups)])
+        self.enc = nn.ModuleList([Stage(ops, in_channels, widths[0], n_stencils, n_conv_per_block, groups, fused_norm)])
         self.pools = nn.ModuleList()
         for i in range(depth):
             self.pools.append(ops.MaxPool())
-            self.enc.append(Stage(ops, widths[i], widths[i + 1], n_stencils, n_conv_per_block, groups))
+            self.enc.append(Stage(ops, widths[i], widths[i + 1], n_stencils, n_conv_per_block, groups, fused_norm))
         self.reduce = nn.ModuleList()
         self.ups = nn.ModuleList()
         self.dec = nn.ModuleList()
         for i in reversed(range(depth)):
-            self.reduce.append(ConvNormAct(ops, widths[i + 1], widths[i + 1] // 2, n_stencils, (1, 1, 1), None))
+            self.reduce.append(ConvNormAct(ops, widths[i + 1], widths[i + 1] // 2, n_stencils, (1, 1, 1), None, fused_norm))
             self.ups.append(ops.UpSampleConst())
-            self.dec.append(Stage(ops, widths[i + 1], widths[i], n_stencils, n_conv_per_block, groups))
+            self.dec.append(Stage(ops, widths[i + 1], widths[i], n_stencils, n_conv_per_block, groups, fused_norm))
         self.head = ops.APRConv(widths[0], out_channels, nstencils=n_stencils, kernel_size=(1, 1, 1))
 
     def forward(self, x, aprs, level_deltas=None):

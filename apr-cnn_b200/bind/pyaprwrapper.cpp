@@ -448,6 +448,41 @@ torch::Tensor upsample_const_backward(std::vector<APR*>& aprs, torch::Tensor gra
     return grad_input;
 }
 
+// ---- fused GroupNorm + ReLU ---------------------------------------------------------------------------
+std::vector<torch::Tensor> groupnorm_relu_forward(torch::Tensor x, c10::optional<torch::Tensor> gamma, c10::optional<torch::Tensor> beta,
+                                                  int64_t groups, double eps, bool relu) {
+    CHECK_INPUT(x);
+    TORCH_CHECK(x.dim() == 3 && x.size(1) % groups == 0, "expected (batch, channels, n) with channels divisible by groups");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto y = torch::empty_like(x);
+    auto mean = torch::empty({x.size(0) * groups}, x.options());
+    auto rstd = torch::empty({x.size(0) * groups}, x.options());
+    auto ws = torch::empty({aprnet_groupnorm_workspace_bytes((int) x.size(0), (int) x.size(1), (int) groups)}, x.options().dtype(torch::kUInt8));
+    const void* g = gamma.has_value() && gamma->defined() ? gamma->contiguous().data_ptr() : nullptr;
+    const void* b = beta.has_value() && beta->defined() ? beta->contiguous().data_ptr() : nullptr;
+    check(aprnet_groupnorm_relu_forward(dtype_id(x), (int) x.size(0), (int) x.size(1), x.size(2), (int) groups, x.data_ptr(), g, b, eps,
+                                        y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), ws.data_ptr(), relu ? 1 : 0, stream_of(x)), "groupnorm_relu_forward");
+    return {y, mean, rstd};
+}
+
+std::vector<torch::Tensor> groupnorm_relu_backward(torch::Tensor x, torch::Tensor grad_y, c10::optional<torch::Tensor> gamma,
+                                                   c10::optional<torch::Tensor> beta, torch::Tensor mean, torch::Tensor rstd,
+                                                   int64_t groups, bool relu) {
+    CHECK_INPUT(x); CHECK_INPUT(grad_y); CHECK_INPUT(mean); CHECK_INPUT(rstd);
+    TORCH_CHECK(x.sizes() == grad_y.sizes(), "grad_y must have the shape of x");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto dx = torch::empty_like(x);
+    auto dgamma = torch::empty({x.size(1)}, x.options());
+    auto dbeta = torch::empty({x.size(1)}, x.options());
+    auto ws = torch::empty({aprnet_groupnorm_workspace_bytes((int) x.size(0), (int) x.size(1), (int) groups)}, x.options().dtype(torch::kUInt8));
+    const void* g = gamma.has_value() && gamma->defined() ? gamma->contiguous().data_ptr() : nullptr;
+    const void* b = beta.has_value() && beta->defined() ? beta->contiguous().data_ptr() : nullptr;
+    check(aprnet_groupnorm_relu_backward(dtype_id(x), (int) x.size(0), (int) x.size(1), x.size(2), (int) groups, x.data_ptr(), grad_y.data_ptr(), g, b,
+                                         mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), ws.data_ptr(),
+                                         relu ? 1 : 0, stream_of(x)), "groupnorm_relu_backward");
+    return {dx, dgamma, dbeta};
+}
+
 // ---- tree fill on (C, N) tensors -------------------------------------------------------------------
 torch::Tensor fill_tree(APR& apr, torch::Tensor input, bool use_max) {
     CHECK_INPUT(input);
@@ -571,6 +606,8 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
     cuda.def("upsample_const_backward", &upsample_const_backward, "aprs"_a, "grad_output"_a, "level_delta"_a);
     cuda.def("restrict_kernel333_forward", &restrict_kernel_333_forward, "weights"_a, "num_levels"_a);
     cuda.def("restrict_kernel333_backward", &restrict_kernel_333_backward, "grad_weights_expanded"_a, "num_levels"_a);
+    cuda.def("groupnorm_relu_forward", &groupnorm_relu_forward, "x"_a, "gamma"_a, "beta"_a, "groups"_a, "eps"_a, "relu"_a);
+    cuda.def("groupnorm_relu_backward", &groupnorm_relu_backward, "x"_a, "grad_y"_a, "gamma"_a, "beta"_a, "mean"_a, "rstd"_a, "groups"_a, "relu"_a);
     // test / inspection hooks (not part of the reference interface)
     cuda.def("fill_tree_mean", &fill_tree_mean_dl, "apr"_a, "input"_a, "level_delta"_a);
     cuda.def("fill_tree_mean_backward", &fill_tree_mean_dl_backward, "apr"_a, "grad_input"_a, "grad_tree"_a, "level_delta"_a);

@@ -203,6 +203,23 @@ int aprnet_conv111_backward_weights_static(const aprnet_apr* apr, int level_delt
                                            void* stream);
 int64_t aprnet_static_scratch_bytes(void);
 
+/* ---- GroupNorm (+ ReLU) over (batch, channels, n) tensors ------------------------------------------
+ * No counterpart among the reference's own kernels: its network blocks call torch.nn.GroupNorm and
+ * ReLU (apr_models/apr_models/unet/unet_parts.py:18-26).  Same arithmetic (biased variance, eps inside
+ * the root, statistics over the whole particle axis of each (batch item, group)), fused into one
+ * statistics pass + one apply pass forward and one reduction pass + one apply pass backward.
+ * x, y, grad tensors are contiguous (batch, channels, n); mean / rstd are (batch * groups); gamma, beta
+ * and their gradients are (channels) or NULL.  relu != 0 fuses max(., 0).
+ * workspace: aprnet_groupnorm_workspace_bytes() bytes. */
+int64_t aprnet_groupnorm_workspace_bytes(int batch, int channels, int groups);
+int aprnet_groupnorm_relu_forward(int dtype, int batch, int channels, int64_t n, int groups, const void* x,
+                                  const void* gamma, const void* beta, double eps, void* y, void* mean, void* rstd,
+                                  void* workspace, int relu, void* stream);
+int aprnet_groupnorm_relu_backward(int dtype, int batch, int channels, int64_t n, int groups, const void* x,
+                                   const void* grad_y, const void* gamma, const void* beta, const void* mean,
+                                   const void* rstd, void* grad_x, void* grad_gamma, void* grad_beta,
+                                   void* workspace, int relu, void* stream);
+
 /* ---- max pooling / constant up-sampling --------------------------------------------------------
  * pyapr/aprnet/cuda/src/maxpool_gpu.hpp:24-40, upsample_constant_gpu.hpp:17-31.
  * maxpool: level_delta -> level_delta + 1; max_indices are int64 positions in the input's particle

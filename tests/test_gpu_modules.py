@@ -125,3 +125,36 @@ def test_unet_step_fp32_and_bf16_agree():
     f32 = torch.cat([g.reshape(-1) for g in grads["fp32"].values()])
     b16 = torch.cat([g.reshape(-1) for g in grads["bf16"].values()])
     assert float(torch.dot(f32, b16) / (f32.norm() * b16.norm())) >= 0.85
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float64, 1e-10), (torch.float32, 2e-5)])
+@pytest.mark.parametrize("b,c,g,n", [(1, 8, 8, 5000), (2, 12, 4, 3001), (1, 32, 32, 70001), (3, 6, 1, 777)])
+def test_groupnorm_relu_matches_torch(b, c, g, n, dtype, tol):
+    """Fused GroupNorm + ReLU against torch.nn.GroupNorm followed by ReLU: output and all gradients."""
+    from pyapr.aprnet import cuda as aprnet
+    dev = torch.device("cuda:0")
+    torch.manual_seed(1)
+    x = (torch.randn(b, c, n, dtype=dtype, device=dev) * 3 + 1).requires_grad_(True)
+    ref = torch.nn.GroupNorm(g, c).to(dev, dtype)
+    mine = aprnet.GroupNormReLU(g, c).to(dev, dtype)
+    with torch.no_grad():
+        ref.weight.uniform_(0.5, 1.5); ref.bias.uniform_(-0.5, 0.5)
+        mine.weight.copy_(ref.weight); mine.bias.copy_(ref.bias)
+    go = torch.randn(b, c, n, dtype=dtype, device=dev)
+    y_ref = torch.relu(ref(x)); y_ref.backward(go)
+    gx_ref, gw_ref, gb_ref = x.grad.clone(), ref.weight.grad.clone(), ref.bias.grad.clone()
+    x.grad = None
+    y = mine(x); y.backward(go)
+    rel = lambda p, q: float((p - q).abs().max() / q.abs().max().clamp_min(1e-30))
+    assert rel(y, y_ref) <= tol
+    assert rel(x.grad, gx_ref) <= tol * 20
+    assert rel(mine.weight.grad, gw_ref) <= tol * 20 and rel(mine.bias.grad, gb_ref) <= tol * 20
+
+
+def test_groupnorm_relu_gradcheck():
+    from pyapr.aprnet import cuda as aprnet
+    dev = torch.device("cuda:0")
+    torch.manual_seed(2)
+    x = (torch.randn(2, 4, 50, dtype=torch.float64, device=dev) + 0.3).requires_grad_(True)
+    m = aprnet.GroupNormReLU(2, 4).double().to(dev)
+    assert gradcheck(lambda t: m(t), (x,), eps=1e-6, atol=1e-6)
