@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <algorithm>
 #include <cstring>
+#include <cstdlib>
 
 namespace {
 
@@ -64,7 +65,11 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
 #ifdef APRNET_TC_DBG_NOLOAD
     return;
 #endif
+#ifdef APRNET_TC_CG
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+#else
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+#endif
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template<int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
@@ -91,6 +96,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (unsigned it = 0; it < SPIN_LIMIT; ++it)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
+}
+// bulk (TMA, non-tensor) copy global -> shared of a contiguous 16-byte-aligned block; completion is
+// signalled on an mbarrier as transferred bytes
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
@@ -232,14 +246,15 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* stage_base = smem;                                            // STAGES * STAGE_BYTES
     int32_t* idx_s = reinterpret_cast<int32_t*>(smem + STAGES * STAGE_BYTES);    // [27][128] source rows
-    uint64_t* bars = reinterpret_cast<uint64_t*>(idx_s + 27 * TILE_M);           // STAGES + 1 mbarriers
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + STAGES + 1);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(idx_s + 27 * TILE_M);           // STAGES (slot free) + 1 (tile done) + STAGES (weights landed)
+    uint64_t* bfull = bars + STAGES + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bfull + STAGES);
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int kchunks = P.kpad / KS;
 
     if (tid == 0) {
-        for (int i = 0; i <= STAGES; ++i) mbar_init(smem_u32(bars + i), 1);
+        for (int i = 0; i <= 2 * STAGES; ++i) mbar_init(smem_u32(bars + i), 1);
         fence_mbar_init();
     }
     if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), NT); tmem_relinquish(); }
@@ -255,10 +270,20 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
                                          : P.segs.tile_begin[P.segs.n]) * P.n_tiles;
     uint32_t gstep = 0;           // stages issued so far by this block (selects buffer and mbarrier phase)
     uint32_t tiles_done = 0;
+    uint32_t bulk_issued = 0;     // stages whose weight copy thread 0 has issued
     bool failed = false;
 
+#ifdef APRNET_TC_DBG_TIMING
+    long long tm[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long t0; int ntl = 0;
+#define TM_START() t0 = clock64()
+#define TM_ADD(i) tm[i] += clock64() - t0
+#else
+#define TM_START()
+#define TM_ADD(i)
+#endif
     for (int work = blockIdx.x; work < total_tiles; work += gridDim.x) {
         const int tile = work / P.n_tiles, ntile = work % P.n_tiles;
+        TM_START();
         ll lo, hi, p;
         int slot, tap_base;
         if (P.edge_mode) {
@@ -297,6 +322,7 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
             }
         }
         __syncthreads();          // source rows are read by other threads of the block
+        TM_ADD(0);
 
         auto issue_loads = [&](int step) {
             const int tap = step / kchunks, kc = step % kchunks;
@@ -314,8 +340,13 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
                 cp_async16(smem_u32(a_s + (j * TILE_M + row) * 16), src);
             }
             // weights of (tap, kc): chunks j in [kc*KS/8, (kc+1)*KS/8), each NT x 16 B, contiguous in global memory
-            const unsigned char* wsrc = reinterpret_cast<const unsigned char*>(wtile + (ll) tap * w_tap_stride + (ll) kc * KS * NT);
-            for (int e = tid; e < B_BYTES / 16; e += TILE_M) cp_async16(smem_u32(b_s + e * 16), wsrc + e * 16);
+            // one bulk copy by one thread (the packed block is contiguous in global memory)
+            if (tid == 0) {
+                const unsigned char* wsrc = reinterpret_cast<const unsigned char*>(wtile + (ll) tap * w_tap_stride + (ll) kc * KS * NT);
+                mbar_expect_tx(smem_u32(bfull + buf), B_BYTES);
+                bulk_copy_g2s(smem_u32(b_s), wsrc, B_BYTES, smem_u32(bfull + buf));
+                bulk_issued = gstep + (uint32_t) step + 1;
+            }
         };
 
         // prologue: fill AHEAD buffers (their previous readers, if any, must have finished)
@@ -332,12 +363,16 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
         }
 
         for (int step = 0; step < steps_per_tile; ++step) {
-            cp_async_wait<AHEAD - 1>();           // this thread's copies of `step` have landed
+            TM_START();
+            cp_async_wait<AHEAD - 1>();
+            TM_ADD(1); TM_START();           // this thread's copies of `step` have landed
             fence_proxy_async();                  // make them visible to the tensor-core (async) proxy
             if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }     // uniform decision for the whole block
             const uint32_t g = gstep + step;
+            TM_ADD(2); TM_START();
 #ifndef APRNET_TC_DBG_NOMMA
             if (tid == 0) {
+                if (!mbar_wait(smem_u32(bfull + g % STAGES), (g / STAGES) & 1)) failed = true;      // weights of this stage
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(stage_base + (g % STAGES) * STAGE_BYTES);
                 const uint32_t b_addr = a_addr + A_BYTES;
@@ -351,6 +386,7 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
                 if (step == steps_per_tile - 1) umma_commit(smem_u32(bars + STAGES));
             }
 #endif
+            TM_ADD(3); TM_START();
             // refill the ring slot last read by the MMAs issued STAGES - AHEAD steps ago
             const int nxt = step + AHEAD;
             if (nxt < steps_per_tile) {
@@ -359,19 +395,23 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
                     const uint32_t use = gn / STAGES;
                     if (!mbar_wait(smem_u32(bars + gn % STAGES), (use - 1) & 1)) failed = true;
                 }
+                TM_ADD(4); TM_START();
                 if (!failed) issue_loads(nxt);
+                TM_ADD(5); TM_START();
             }
             cp_async_commit();
         }
         gstep += steps_per_tile;
-        if (failed) break;
+        if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }
 
         // epilogue: accumulators -> registers -> global (coalesced along the particle axis)
+        TM_START();
         {
             const bool ok = mbar_wait(smem_u32(bars + STAGES), tiles_done & 1);
             if (__syncthreads_or(ok ? 0 : 1)) { failed = true; break; }
         }
         ++tiles_done;
+        TM_ADD(6); TM_START();
         tc_fence_after();
 #pragma unroll
         for (int c0 = 0; c0 < NT; c0 += 32) {
@@ -394,10 +434,21 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
         }
         tc_fence_before();
         __syncthreads();          // all TMEM reads done before the next tile's first MMA overwrites D
+        TM_ADD(7);
+#ifdef APRNET_TC_DBG_TIMING
+        ++ntl;
+#endif
     }
+#ifdef APRNET_TC_DBG_TIMING
+    if (blockIdx.x == 7 && (tid == 0 || tid == 77)) printf("tid %d tiles %d steps/tile %d | idx %lld | cpwait %lld | fence+bar %lld | mma %lld | mbarwait %lld | issue %lld | epi-wait %lld | epi %lld (cycles per tile)\n", tid, ntl, steps_per_tile, tm[0]/ntl, tm[1]/ntl, tm[2]/ntl, tm[3]/ntl, tm[4]/ntl, tm[5]/ntl, tm[6]/ntl, tm[7]/ntl);
+#endif
 
     // teardown (also the error path): drain copies, release TMEM
     cp_async_wait<0>();
+    if (failed && tid == 0) {      // bulk copies still in flight must land before the block's shared memory is released
+        for (uint32_t g = bulk_issued > STAGES ? bulk_issued - STAGES : 0; g < bulk_issued; ++g)
+            mbar_wait(smem_u32(bfull + g % STAGES), (g / STAGES) & 1);
+    }
     if (failed && P.error_flag) *P.error_flag = 1;
     tc_fence_before();
     __syncthreads();
@@ -441,13 +492,19 @@ TcGeom tc_geometry(ll rows, int k_dim, int n_dim, int slots) {
 
 template<int NT, int KS>
 int launch_tc(const TcParams& P, int total_tiles, cudaStream_t st, const char* pname) {
-    const size_t smem = (size_t) STAGES * (TILE_M * KS * 2 + NT * KS * 2) + 27 * TILE_M * 4 + (STAGES + 1) * 8 + 16;
+    const size_t smem = (size_t) STAGES * (TILE_M * KS * 2 + NT * KS * 2) + 27 * TILE_M * 4 + (2 * STAGES + 1) * 8 + 16;
     auto kern = conv333_tc_kernel<NT, KS>;
     APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int per_sm = std::max(1, std::min(std::min(4, 512 / NT), (int) (225 * 1024 / (smem + 1024))));
+    int per_sm = std::max(1, std::min(std::min(4, 512 / NT), (int) (225 * 1024 / (smem + 1024))));
+    // tuning knobs (environment): blocks per SM and the shared-memory carve-out in percent; the part of the
+    // 256 KB array that is not carved out for shared memory serves as L1 for the cp.async.ca gathers
+    if (const char* e = getenv("APRNET_TC_BLOCKS_PER_SM")) per_sm = std::max(1, std::min(per_sm, atoi(e)));
+    int carve = -1;
+    if (const char* e = getenv("APRNET_TC_CARVEOUT")) carve = atoi(e);
+    if (carve >= 0) APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, carve));
     const int grid = std::min(total_tiles, sms * per_sm);
     { AprnetProfScope _prof(pname, st);
     kern<<<grid, TILE_M, smem, st>>>(P);

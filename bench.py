@@ -131,35 +131,54 @@ def unet_conv_layers(base, depth):
     return layers
 
 
-def roofline_from_profile(prof, steps, nparts, ntree, peaks, layers):
-    """Roofline entry of the kernel that took the most time in the timed region.
+def roofline_from_profile(prof, steps, nparts, ntree, peaks, layers, bf16):
+    """Roofline entry of the convolution kernel that took the most time in the timed region.
 
-    Kernel names carry their shape: `conv333_fwd:ci32:co32:dl0`.  One "launch" below is one operator
-    call on one APR (the weight-gradient kernel runs once per level inside it; those launches are
-    summed).  Algorithmic work of one call: flops = 54 * cin * cout * N(dl);
-    bytes = (4 cin + 4 cout) * N + 2 N + 8 cin * T (tree scratch written and read once).  The bound is
-    the tensor pipe when flops/bytes exceeds the ridge of the measured peaks, HBM otherwise."""
+    Kernel names carry their shape: `conv333_tc_dw:ci32:co32:dl0`.  All shapes of one kernel function
+    (the part of the name before the first colon) form one family; the family with the largest total
+    time is reported, its launches summed.  Algorithmic work of one 3x3x3 operator call on one APR:
+    flops = 54 * cin * cout * N(dl) for the forward pass, the same-level input gradient and the weight
+    gradient alike; bytes = (e_in * cin + 4 * cout) * N + 2 * N + e_in * cin * T, with e_in = 2 on the
+    bf16 path (packed rows) and 4 on the fp32 path, N the particles of that level_delta, T the tree
+    nodes, 2 * N the y coordinates of the access structure.  The bound is the tensor pipe when
+    flops/bytes exceeds the ridge of the measured peaks, HBM otherwise."""
     if not prof:
         return None
-    name, (calls, ms) = max(prof.items(), key=lambda kv: kv[1][1])
-    parts = name.split(":")
-    rf = {"kernel": name, "share_of_profiled": ms / sum(v[1] for v in prof.values())}
-    if parts[0].startswith("conv333") and len(parts) == 4 and parts[1].startswith("ci"):
-        cin, cout, dl = int(parts[1][2:]), int(parts[2][2:]), int(parts[3][2:])
-        n_ops = max(1, sum(1 for k, ci, co, d in layers if k == "333" and (ci, co, d) == (cin, cout, dl))) * steps
+    total_ms = sum(v[1] for v in prof.values())
+    fams = {}
+    for name, (calls, ms) in prof.items():
+        parts = name.split(":")
+        if len(parts) == 4 and parts[0].startswith("conv333") and parts[0] != "conv333_tc_edge" and parts[1].startswith("ci"):
+            fams.setdefault(parts[0], []).append((int(parts[1][2:]), int(parts[2][2:]), int(parts[3][2:]), calls, ms))
+    if not fams:
+        name, (calls, ms) = max(prof.items(), key=lambda kv: kv[1][1])
+        return {"kernel": name, "share_of_profiled": ms / total_ms}
+    fam, rows = max(fams.items(), key=lambda kv: sum(r[4] for r in kv[1]))
+    e_in = 2.0 if bf16 else 4.0
+    flops = byts = ms_sum = 0.0
+    launches = ops = 0
+    for cin, cout, dl, calls, ms in rows:
+        # the tensor-core kernels run once per operator call; the fp32 weight gradient runs once per level
+        n_ops = calls if fam.startswith("conv333_tc") or fam != "conv333_dw" else \
+            max(1, sum(1 for k, ci, co, d in layers if k == "333" and (ci, co, d) == (cin, cout, dl))) * steps
         n, t = nparts[dl], ntree[dl]
-        flops = 54.0 * cin * cout * n
-        byts = (4.0 * cin + 4.0 * cout + 2.0) * n + 8.0 * cin * t
-        ridge = peaks["tflops"] * 1e12 / (peaks["hbm_gbs"] * 1e9)
-        sec = ms / n_ops * 1e-3
-        rf.update(launches_per_call=calls / n_ops, avg_ms=ms / n_ops)
-        if flops / byts > ridge:
-            ach = flops / sec / 1e12
-            rf.update(bound="tensor", achieved=ach, peak=peaks["tflops"], unit="TFLOP/s", frac=ach / peaks["tflops"])
-        else:
-            ach = byts / sec / 1e9
-            rf.update(bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"])
-        rf.update(algorithmic_flops=flops, algorithmic_bytes=byts, peak_source=peaks["source"], traffic=None)
+        flops += n_ops * 54.0 * cin * cout * n
+        byts += n_ops * ((e_in * cin + 4.0 * cout + 2.0) * n + e_in * cin * t)
+        ms_sum += ms
+        launches += calls
+        ops += n_ops
+    sec = ms_sum * 1e-3
+    ridge = peaks["tflops"] * 1e12 / (peaks["hbm_gbs"] * 1e9)
+    rf = {"kernel": fam, "shapes": len(rows), "launches": launches, "operator_calls": ops,
+          "share_of_profiled": ms_sum / total_ms, "avg_ms": ms_sum / max(1, launches)}
+    if flops / byts > ridge:
+        ach = flops / sec / 1e12
+        rf.update(bound="tensor", achieved=ach, peak=peaks["tflops"], unit="TFLOP/s", frac=ach / peaks["tflops"])
+    else:
+        ach = byts / sec / 1e9
+        rf.update(bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"])
+    rf.update(algorithmic_flops_per_launch=flops / max(1, launches), algorithmic_bytes_per_launch=byts / max(1, launches),
+              hbm_gbs_at_algorithmic_bytes=byts / sec / 1e9, peak_source=peaks["source"], traffic=None)
     return rf
 
 
@@ -349,7 +368,7 @@ def run_gpu(args):
     if e2e_ms_all:
         out["e2e"] = {"value": n_total / (e2e_ms_all / args.steps * 1e-3), "unit": "particles/s",
                       "h2d_bytes_per_step": int(x_host.numel() * 4 + y_host.numel() * 8), "d2h_bytes_per_step": 4}
-    out["roofline"] = roofline_from_profile(prof, args.steps, nparts, o_tree, peaks, unet_conv_layers(args.base, args.depth))
+    out["roofline"] = roofline_from_profile(prof, args.steps, nparts, o_tree, peaks, unet_conv_layers(args.base, args.depth), args.dtype == "bf16")
     if world == 1 and not args.no_cpu_baseline:
         cb = run_cpu(args, 1, 1)
         out["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
