@@ -146,6 +146,17 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo, uint
     return (uint64_t) ((saddr >> 4) & 0x3FFF) | ((uint64_t) ((lbo >> 4) & 0x3FFF) << 16) |
            ((uint64_t) ((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46);
 }
+// K-major operand stored with a hardware swizzle: rows of 32/64/128 bytes, 8-row atoms `sbo` bytes apart;
+// layout 2 = 128-byte, 4 = 64-byte, 6 = 32-byte swizzle.  The 16-byte chunk c of row r sits at chunk
+// position c ^ f(r) (address bits [4,7) xor-ed with bits [7,10), restricted to the swizzle width).  A K
+// step of 16 elements advances the start address by 32 bytes inside the atom.
+__device__ __forceinline__ uint64_t make_desc_swizzled(uint32_t saddr, uint32_t sbo, uint32_t layout) {
+    return (uint64_t) ((saddr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t) ((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46) |
+           ((uint64_t) layout << 61);
+}
+template<int KS> __device__ __forceinline__ int swizzled_chunk(int row, int c) {
+    return KS == 64 ? (c ^ (row & 7)) : (KS == 32 ? (c ^ ((row >> 1) & 3)) : (c ^ ((row >> 2) & 1)));
+}
 // Instruction descriptor: D fp32, A/B bf16, both K-major, M = 128, N = n
 __host__ __device__ constexpr uint32_t make_idesc(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (TILE_M >> 4) << 24);
@@ -455,6 +466,284 @@ __global__ void __launch_bounds__(TILE_M) conv333_tc_kernel(const TcParams P) {
     if (warp == 0) tmem_dealloc(tmem_d, NT);
 }
 
+// ---- warp-specialised gather kernel ---------------------------------------------------------------
+// One persistent block per SM, 14 warps (forward pass and same-level input gradient):
+//   warps 0-7   producers.  A stage (one tap, KS channels, 128 rows) belongs to ONE warp: warp w fills the
+//               stages w, w + 8, w + 16 ... of the block's stage sequence, so eight stages are being issued
+//               at once and the per-stage bookkeeping (slot wait, weight copy, barrier arrival) is paid
+//               once per 4 * KS / 8 copy instructions.  Lane 0 streams the stage's weight tile with one bulk
+//               copy (byte-counting arrival); every lane attaches an asynchronous arrival to the stage's
+//               barrier (cp.async.mbarrier.arrive.noinc), so the stage is handed to the MMA warp the moment
+//               its copies land.  Producers only block on a ring slot the tensor core still reads;
+//   warp 8      one thread issues the tcgen05.mma of each stage, in stage order, as soon as its barrier
+//               completes, and commits the stage's "slot free" barrier; accumulators rotate through
+//               NACC TMEM buffers so that later tiles start while earlier ones are read back;
+//   warps 10-13 epilogue: TMEM -> registers -> global for tile i; the neighbour-table entries of tile
+//               i + NIDX are requested into registers before the wait for tile i and decoded into the
+//               source-row buffer tile i has released afterwards, so their DRAM latency is never exposed.
+// All waits are bounded and poll a block-wide abort flag.
+constexpr int WS_NPROD = 8;
+constexpr int WS_THREADS = (WS_NPROD + 6) * 32;
+constexpr int WS_MAX_STAGES = 20;
+constexpr int WS_MAX_ACC = 4;
+constexpr int WS_NIDX = 3;
+
+struct TileInfo { ll lo, hi, p0; int slot, ntile; };
+
+__device__ __forceinline__ TileInfo tile_info(const TcParams& P, int work) {
+    TileInfo t;
+    const int tile = P.n_tiles == 1 ? work : work / P.n_tiles;
+    t.ntile = P.n_tiles == 1 ? 0 : work % P.n_tiles;
+    int seg = 0;
+    while (seg + 1 < P.segs.n && tile >= P.segs.tile_begin[seg + 1]) ++seg;
+    t.lo = P.segs.begin[seg]; t.hi = P.segs.end[seg];
+    t.p0 = t.lo + (ll) (tile - P.segs.tile_begin[seg]) * TILE_M;
+    t.slot = P.segs.slot[seg];
+    return t;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool ws_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63) == 63 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+// one lane polls, the warp follows
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = ws_wait(bar, parity, abort_flag) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
+}
+// arrival on an mbarrier that is triggered when all earlier cp.async copies of this thread have completed
+// (counts as one of the barrier's expected arrivals)
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+
+template<int NT, int KS, int NACC>
+__global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcParams P, const int stages) {
+    // A operand: K-major with the hardware swizzle whose width equals the row piece of one stage (KS
+    // channels = 32, 64 or 128 bytes).  A gathered row piece is then contiguous in shared memory as it is
+    // in global memory (its 16-byte chunks permuted inside the piece), so the lanes that copy one piece
+    // write one contiguous block; with the unswizzled layout every 16-byte chunk of a row goes to a
+    // different plane and each 32-byte sector costs its own pass of the shared-memory write pipe.
+    constexpr int NIDX = WS_NIDX;
+    constexpr int CH = KS / 8;                               // 16-byte chunks per gathered row piece
+    constexpr int RW = 32 / CH;                              // rows covered by one copy instruction of a warp
+    constexpr int NI = TILE_M / RW;                          // copy instructions per stage
+    constexpr int ROW_BYTES = KS * 2;
+    constexpr uint32_t A_LAYOUT = KS == 64 ? 2u : (KS == 32 ? 4u : 6u);     // SWIZZLE_128B / 64B / 32B
+    constexpr int A_BYTES = TILE_M * ROW_BYTES;
+    constexpr int B_BYTES = NT * KS * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t IDESC = make_idesc(NT);
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    // swizzle atoms (8 rows) must start on a multiple of their size: align the ring to 1024 bytes
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned char* stage_base = smem;
+    int32_t* idx_s = reinterpret_cast<int32_t*>(smem + (size_t) stages * STAGE_BYTES);      // NIDX x [27][128] source rows
+    uint64_t* bars = reinterpret_cast<uint64_t*>(idx_s + NIDX * 27 * TILE_M);
+    uint64_t* full = bars;                          // [stages]  copies of the stage landed (32 lanes + weight bytes)
+    uint64_t* empty = bars + WS_MAX_STAGES;         // [stages]  MMAs that read the stage completed
+    uint64_t* tmem_full = empty + WS_MAX_STAGES;    // [NACC]    accumulator complete
+    uint64_t* tmem_empty = tmem_full + WS_MAX_ACC;  // [NACC]    accumulator read back (one arrival per epilogue warp)
+    uint64_t* idx_full = tmem_empty + WS_MAX_ACC;   // [NIDX]    source rows of a tile written (one arrival per epilogue warp)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(idx_full + WS_MAX_ACC);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kchunks = P.kpad / KS;
+    const int steps_per_tile = 27 * kchunks;
+    const int total_tiles = P.segs.tile_begin[P.segs.n] * P.n_tiles;
+    const int my_tiles = (int) blockIdx.x < total_tiles ? (total_tiles - (int) blockIdx.x + (int) gridDim.x - 1) / (int) gridDim.x : 0;
+    const int nprod = min(WS_NPROD, stages);
+
+    if (tid == 0) {
+        for (int i = 0; i < stages; ++i) { mbar_init(smem_u32(full + i), 32 + 1); mbar_init(smem_u32(empty + i), 1); }
+        for (int i = 0; i < NACC; ++i) { mbar_init(smem_u32(tmem_full + i), 1); mbar_init(smem_u32(tmem_empty + i), 4); }
+        for (int i = 0; i < NIDX; ++i) mbar_init(smem_u32(idx_full + i), 4);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == WS_NPROD) { tmem_alloc(smem_u32(tmem_slot), NACC * NT); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_d = *tmem_slot;
+    bool failed = false;
+    bool bulk_issued = false;
+#ifdef APRNET_TC_DBG_TIMING
+    long long wt[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long w0 = clock64(); const long long wstart = w0;
+#define WT(i) { const long long w1 = clock64(); wt[i] += w1 - w0; w0 = w1; }
+#else
+#define WT(i)
+#endif
+
+    if (warp < WS_NPROD) {
+        // ---------------- producers ----------------
+        if (warp < nprod) {
+            const int j = lane % CH, r0 = lane / CH;
+            const uint32_t total_stages = (uint32_t) my_tiles * (uint32_t) steps_per_tile;
+            uint32_t g = warp, slot = warp, use = 0;       // nprod <= stages: the first stage of every warp has its own slot
+            int it = 0, step = warp, cur_it = -1;
+            const int32_t* idx = idx_s;
+            const unsigned char* wsrc = nullptr;
+            const ll w_tap_stride = (ll) P.n_tiles * P.kpad * NT * 2;
+            while (g < total_stages) {
+                while (step >= steps_per_tile) { step -= steps_per_tile; ++it; }
+                if (it != cur_it) {
+                    cur_it = it;
+                    WT(7);
+                    if (!warp_wait(smem_u32(idx_full + it % NIDX), (it / NIDX) & 1, abort_flag)) { failed = true; break; }
+                    WT(0);
+                    idx = idx_s + (it % NIDX) * 27 * TILE_M;
+                    if (lane == 0) {      // packed weights of one (slot, tap, n tile) are [k chunk][n][8]; a stage takes KS / 8 chunks
+                        const TileInfo ti = tile_info(P, blockIdx.x + it * gridDim.x);
+                        wsrc = reinterpret_cast<const unsigned char*>(P.wp + ((ll) ti.slot * 27 * P.n_tiles + ti.ntile) * ((ll) P.kpad * NT));
+                    }
+                }
+                const int tap = step / kchunks, kc = step - tap * kchunks;
+                if (use > 0 && !warp_wait(smem_u32(empty + slot), (use - 1) & 1, abort_flag)) { failed = true; break; }
+                WT(1);
+                unsigned char* a_s = stage_base + (size_t) slot * STAGE_BYTES;
+                if (lane == 0) {
+                    mbar_expect_tx(smem_u32(full + slot), B_BYTES);
+                    bulk_copy_g2s(smem_u32(a_s + A_BYTES), wsrc + (ll) tap * w_tap_stride + (ll) kc * KS * NT * 2, B_BYTES, smem_u32(full + slot));
+                    bulk_issued = true;
+                }
+                const int32_t* idx_t = idx + tap * TILE_M + r0;
+                const __nv_bfloat16* src0 = P.rows + kc * KS + j * 8;
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    const int row = i * RW + r0;
+                    cp_async16(smem_u32(a_s + row * ROW_BYTES + (swizzled_chunk<KS>(row, j) << 4)), src0 + (ll) idx_t[i * RW] * P.kpad);
+                }
+                WT(2);
+                // the stage's barrier receives this thread's arrival when the copies above have landed
+                cp_async_arrive_noinc(smem_u32(full + slot));
+                WT(3);
+                g += nprod; step += nprod; slot += nprod;
+                if (slot >= (uint32_t) stages) { slot -= stages; ++use; }
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+        }
+    } else if (warp == WS_NPROD) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            uint32_t slot = 0, use = 0;
+            for (int it = 0; it < my_tiles && !failed; ++it) {
+                const uint32_t acc = (uint32_t) it % NACC, acc_use = (uint32_t) it / NACC;
+                if (acc_use > 0 && !ws_wait(smem_u32(tmem_empty + acc), (acc_use - 1) & 1, abort_flag)) { failed = true; break; }
+                tc_fence_after();
+                WT(0);
+                for (int step = 0; step < steps_per_tile; ++step) {
+                    if (!ws_wait(smem_u32(full + slot), use & 1, abort_flag)) { failed = true; break; }
+                    WT(1);
+                    fence_proxy_async();          // generic-proxy writes of the cp.async copies -> tensor-core (async proxy) reads
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(stage_base + (size_t) slot * STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < KS / 16; ++k) {
+                        const uint64_t da = make_desc_swizzled(a_addr + k * 32, 8 * ROW_BYTES, A_LAYOUT);
+                        const uint64_t db = make_desc(b_addr + k * 2 * (NT * 16), NT * 16, 128);
+                        umma_bf16(tmem_d + acc * NT, da, db, IDESC, (step > 0 || k > 0) ? 1u : 0u);
+                    }
+                    WT(2);
+                    umma_commit(smem_u32(empty + slot));
+                    WT(3);
+                    if (++slot == (uint32_t) stages) { slot = 0; ++use; }
+                }
+                if (!failed) umma_commit(smem_u32(tmem_full + acc));
+            }
+        }
+    } else if (warp >= WS_NPROD + 2) {
+        // ---------------- epilogue + source-row staging ----------------
+        const int q = warp & 3;                           // TMEM lane group this warp may read
+        const int row = q * 32 + lane;
+        int32_t v[27];
+        auto request_idx = [&](int it) {                  // table entries of this thread's row of tile `it` -> registers
+            if (it >= my_tiles) return;
+            const TileInfo ti = tile_info(P, blockIdx.x + it * gridDim.x);
+            const ll p = ti.p0 + row;
+#pragma unroll
+            for (int tap = 0; tap < 27; ++tap) v[tap] = (p < ti.hi) ? __ldg(P.nbr + (ll) tap * P.N + p) : APRNET_NONE;
+        };
+        auto publish_idx = [&](int it) {                  // decode and hand the rows to the producers
+            if (it >= my_tiles) return;
+            const TileInfo ti = tile_info(P, blockIdx.x + it * gridDim.x);
+            int32_t* dst = idx_s + (it % NIDX) * 27 * TILE_M;
+#pragma unroll
+            for (int tap = 0; tap < 27; ++tap) {
+                ll r = P.zero_row;
+                if (P.same_level_only) { if (v[tap] >= ti.lo && v[tap] < ti.hi) r = v[tap]; }
+                else if (v[tap] >= 0) r = v[tap];
+                else if (v[tap] != APRNET_NONE) r = P.tree_base + aprnet_dec_tree(v[tap]);
+                dst[tap * TILE_M + row] = (int32_t) r;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(idx_full + it % NIDX));
+        };
+        for (int it = 0; it < NIDX; ++it) { request_idx(it); publish_idx(it); }
+        for (int it = 0; it < my_tiles; ++it) {
+            WT(7);
+            const TileInfo ti = tile_info(P, blockIdx.x + it * gridDim.x);
+            const ll p = ti.p0 + row;
+            const bool valid = p < ti.hi;
+            const uint32_t acc = (uint32_t) it % NACC, acc_use = (uint32_t) it / NACC;
+            request_idx(it + NIDX);       // lands while this warp waits for the accumulator
+            WT(2);
+            if (!warp_wait(smem_u32(tmem_full + acc), acc_use & 1, abort_flag)) { failed = true; break; }
+            WT(0);
+            tc_fence_after();
+#pragma unroll
+            for (int c0 = 0; c0 < NT; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_d + ((uint32_t) (q * 32) << 16) + acc * NT + c0, r);
+                tmem_ld_wait();
+                if (valid) {
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj) {
+                        const int n = ti.ntile * NT + c0 + jj;
+                        if (n < P.n_dim) P.out[(ll) n * P.ld_out + p] = __uint_as_float(r[jj]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(tmem_empty + acc));
+            WT(1);
+            // every copy that read the source rows of tile `it` has landed (its accumulator is complete)
+            publish_idx(it + NIDX);
+            WT(3);
+        }
+    }
+
+#ifdef APRNET_TC_DBG_TIMING
+    if (blockIdx.x == 7 && (tid == 0 || tid == 32 * WS_NPROD || tid == 32 * (WS_NPROD + 2))) {
+        const long long tot = clock64() - wstart;
+        printf("ws tid %d total %lld | %lld %lld %lld %lld %lld %lld %lld %lld | stages %d nacc %d tiles %d steps/tile %d\n", tid, tot, wt[0], wt[1], wt[2], wt[3], wt[4], wt[5], wt[6], wt[7], stages, NACC, my_tiles, steps_per_tile);
+    }
+#endif
+    // teardown (also the error path): the gather copies were drained above; after a failure the bulk
+    // copies still in flight get time to land before the block's shared memory is released
+    if (failed) {
+        *abort_flag = 1;
+        if (P.error_flag) *P.error_flag = 1;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (bulk_issued && *abort_flag) for (int i = 0; i < 2000; ++i) __nanosleep(100);
+    if (warp == WS_NPROD) tmem_dealloc(tmem_d, NACC * NT);
+}
+
 __global__ void set_group_tile_begin_kernel(EdgeGroupDev* g, int n, int tile) {
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         int acc = 0;
@@ -482,8 +771,8 @@ struct TcGeom { int kpad, ks, nt, n_tiles; size_t rows_bytes, w_bytes; };
 TcGeom tc_geometry(ll rows, int k_dim, int n_dim, int slots) {
     TcGeom g;
     g.kpad = pad_to(k_dim, 16);
-    g.ks = (g.kpad % 32 == 0) ? 32 : 16;
     g.nt = pick_nt(n_dim);
+    g.ks = (g.kpad % 64 == 0 && g.nt <= 128) ? 64 : ((g.kpad % 32 == 0) ? 32 : 16);
     g.n_tiles = (n_dim + g.nt - 1) / g.nt;
     g.rows_bytes = ((size_t) rows * g.kpad * 2 + 255) / 256 * 256;
     g.w_bytes = ((size_t) slots * 27 * g.n_tiles * g.kpad * g.nt * 2 + 255) / 256 * 256;
@@ -513,10 +802,42 @@ int launch_tc(const TcParams& P, int total_tiles, cudaStream_t st, const char* p
     return APRNET_OK;
 }
 
+template<int NT, int KS>
+int launch_tc_ws(const TcParams& P, int total_tiles, cudaStream_t st, const char* pname) {
+    constexpr size_t STAGE = (size_t) TILE_M * KS * 2 + (size_t) NT * KS * 2;
+    constexpr size_t FIXED = (size_t) WS_NIDX * 27 * TILE_M * 4 + (2 * WS_MAX_STAGES + 3 * WS_MAX_ACC) * 8 + 16 + 1024;      // + alignment slack
+    constexpr int NACC = NT <= 128 ? 4 : 2;          // accumulators in flight: the SM's 512 TMEM columns, at most 4
+    auto kern = conv333_tc_ws_kernel<NT, KS, NACC>;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // one block per SM with all of its shared memory (227 KB, 1 KB reserved) as the stage ring
+    int stages = (int) std::min<size_t>(WS_MAX_STAGES, (227 * 1024 - 1024 - FIXED) / STAGE);
+    if (const char* e = getenv("APRNET_TC_WS_STAGES")) stages = std::max(2, std::min(stages, atoi(e)));
+    if (stages < 2) { aprnet_set_error("conv333 tensor-core path: tile nt=%d ks=%d does not fit shared memory", NT, KS); return APRNET_ERR_UNSUPPORTED; }
+    const size_t smem = (size_t) stages * STAGE + FIXED;
+    APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    const int grid = std::min(total_tiles, sms);
+    { AprnetProfScope _prof(pname, st);
+    kern<<<grid, WS_THREADS, smem, st>>>(P, stages);
+    }
+    APRNET_LAUNCH_CHECK();
+    return APRNET_OK;
+}
+
 int dispatch_tc(const TcParams& P, const TcGeom& g, int total_tiles, cudaStream_t st, const char* pname) {
-#define TC_CASE(NT_, KS_) if (g.nt == NT_ && g.ks == KS_) return launch_tc<NT_, KS_>(P, total_tiles, st, pname);
-    TC_CASE(32, 16) TC_CASE(32, 32) TC_CASE(64, 16) TC_CASE(64, 32) TC_CASE(128, 16) TC_CASE(128, 32) TC_CASE(256, 16) TC_CASE(256, 32)
+    static const bool legacy = getenv("APRNET_TC_LEGACY") != nullptr;
+    if (legacy || P.edge_mode) {          // the edge-list GEMM (one or a few stages per tile) stays on the block-synchronous kernel
+        const int ks = std::min(g.ks, 32);
+#define TC_CASE(NT_, KS_) if (g.nt == NT_ && ks == KS_) return launch_tc<NT_, KS_>(P, total_tiles, st, pname);
+        TC_CASE(32, 16) TC_CASE(32, 32) TC_CASE(64, 16) TC_CASE(64, 32) TC_CASE(128, 16) TC_CASE(128, 32) TC_CASE(256, 16) TC_CASE(256, 32)
 #undef TC_CASE
+    } else {
+#define TC_CASE(NT_, KS_) if (g.nt == NT_ && g.ks == KS_) return launch_tc_ws<NT_, KS_>(P, total_tiles, st, pname);
+        TC_CASE(32, 16) TC_CASE(32, 32) TC_CASE(32, 64) TC_CASE(64, 16) TC_CASE(64, 32) TC_CASE(64, 64)
+        TC_CASE(128, 16) TC_CASE(128, 32) TC_CASE(128, 64) TC_CASE(256, 16) TC_CASE(256, 32)
+#undef TC_CASE
+    }
     aprnet_set_error("conv333 tensor-core path: unsupported tile geometry nt=%d ks=%d", g.nt, g.ks);
     return APRNET_ERR_UNSUPPORTED;
 }
@@ -563,6 +884,7 @@ int aprnet_tc_gather_conv(aprnet_apr* a, int dl, int backward, int cin, int cout
     P.wp = wp; P.out = out; P.ld_out = ld_out; P.n_dim = n_dim; P.n_tiles = g.n_tiles; P.same_level_only = backward;
     P.error_flag = g_error_flag_dev;
     P.edge_mode = 0; P.edge_src = nullptr; P.groups = nullptr; P.n_groups = 0; P.edge_origin = 0; P.out_rows = nullptr; P.row_pad = 0;
+
     const int total = P.segs.tile_begin[P.segs.n] * g.n_tiles;
     if (total == 0) return APRNET_OK;
     char pname[64];

@@ -158,9 +158,9 @@ def roofline_from_profile(prof, steps, nparts, ntree, peaks, layers, bf16):
     flops = byts = ms_sum = 0.0
     launches = ops = 0
     for cin, cout, dl, calls, ms in rows:
-        # the tensor-core kernels run once per operator call; the fp32 weight gradient runs once per level
-        n_ops = calls if fam.startswith("conv333_tc") or fam != "conv333_dw" else \
-            max(1, sum(1 for k, ci, co, d in layers if k == "333" and (ci, co, d) == (cin, cout, dl))) * steps
+        # the gather kernels run once per operator call; the weight-gradient kernels run once per level
+        n_ops = max(1, sum(1 for k, ci, co, d in layers if k == "333" and (ci, co, d) == (cin, cout, dl))) * steps \
+            if fam in ("conv333_dw", "conv333_tc_dw") else calls
         n, t = nparts[dl], ntree[dl]
         flops += n_ops * 54.0 * cin * cout * n
         byts += n_ops * ((e_in * cin + 4.0 * cout + 2.0) * n + e_in * cin * t)
