@@ -232,7 +232,8 @@ std::vector<torch::Tensor> conv333_forward_keep_tree(std::vector<APR*>& aprs, to
 }
 
 static std::vector<torch::Tensor> conv333_backward_impl(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights,
-                                            torch::Tensor grad_output, torch::Tensor level_delta, c10::optional<torch::Tensor> saved_tree) {
+                                            torch::Tensor grad_output, torch::Tensor level_delta, c10::optional<torch::Tensor> saved_tree,
+                                            bool need_grad_input = true) {
     CHECK_INPUT(input); CHECK_INPUT(weights); CHECK_INPUT(grad_output);
     check_batch(aprs, input);
     TORCH_CHECK(grad_output.dim() == 3 && grad_output.size(0) == input.size(0) && grad_output.size(1) == weights.size(1) &&
@@ -249,13 +250,14 @@ static std::vector<torch::Tensor> conv333_backward_impl(std::vector<APR*>& aprs,
     const int dt = dtype_id(input);
     void* st = stream_of(input);
     const bool tc = g_conv_mode == 1 && dt == APRNET_F32;
+    const bool skip_gin = tc && !need_grad_input;        // only the tensor-core driver can leave the input gradient out
     const bool have_tree = saved_tree.has_value() && saved_tree->defined() && saved_tree->dim() == 3 && saved_tree->size(0) == input.size(0) &&
                            saved_tree->size(1) == cin && saved_tree->size(2) == max_tree && saved_tree->is_contiguous() &&
                            saved_tree->scalar_type() == input.scalar_type();
     auto tree_all = have_tree ? *saved_tree : torch::empty({1, cin, max_tree}, input.options());
     auto grad_tree = torch::empty({cin, max_tree}, input.options());
     // the tensor-core path writes every valid entry of grad_input; the CUDA-core path accumulates into zeros
-    auto grad_input = tc ? torch::empty_like(input) : torch::zeros_like(input);
+    auto grad_input = skip_gin ? torch::Tensor() : (tc ? torch::empty_like(input) : torch::zeros_like(input));
     auto grad_weights = torch::zeros_like(weights);
     torch::Tensor partial;
     if (!tc) partial = torch::empty({aprnet_conv333_partial_elems((int) cin, (int) cout)}, input.options());
@@ -274,11 +276,11 @@ static std::vector<torch::Tensor> conv333_backward_impl(std::vector<APR*>& aprs,
         if (tc) {
             check(aprnet_conv333_backward_tc(h, dl[b], (int) cin, (int) cout, (int) weights.size(0), (const float*) row(input, b), n,
                                              (const float*) row(grad_output, b), n, (const float*) weights.data_ptr(),
-                                             (float*) row(grad_input, b), (float*) grad_weights.data_ptr(), (float*) tree.data_ptr(),
+                                             skip_gin ? nullptr : (float*) row(grad_input, b), (float*) grad_weights.data_ptr(), (float*) tree.data_ptr(),
                                              have_tree ? 1 : 0, (float*) grad_tree.data_ptr(), max_tree, (float*) partial_tc.data_ptr(),
                                              ws.data_ptr(), st),
                   "conv333_backward (tensor cores)");
-            zero_padding(grad_input, b, aprs[b]->number_parts(dl[b]));
+            if (!skip_gin) zero_padding(grad_input, b, aprs[b]->number_parts(dl[b]));
             continue;
         }
         if (!have_tree)
@@ -299,8 +301,9 @@ std::vector<torch::Tensor> conv333_backward(std::vector<APR*>& aprs, torch::Tens
 }
 
 std::vector<torch::Tensor> conv333_backward_with_tree(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights,
-                                                      torch::Tensor grad_output, torch::Tensor level_delta, torch::Tensor tree) {
-    return conv333_backward_impl(aprs, input, weights, grad_output, level_delta, tree);
+                                                      torch::Tensor grad_output, torch::Tensor level_delta, torch::Tensor tree,
+                                                      bool need_grad_input) {
+    return conv333_backward_impl(aprs, input, weights, grad_output, level_delta, tree, need_grad_input);
 }
 
 // ---- 1x1x1 convolution ------------------------------------------------------------------------
@@ -601,7 +604,7 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
     cuda.def("conv333_backward", &conv333_backward, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a);
     // extensions: keep the tree means of the forward pass for the backward pass
     cuda.def("conv333_forward_keep_tree", &conv333_forward_keep_tree, "aprs"_a, "input"_a, "weights"_a, "level_delta"_a);
-    cuda.def("conv333_backward_with_tree", &conv333_backward_with_tree, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a, "tree"_a);
+    cuda.def("conv333_backward_with_tree", &conv333_backward_with_tree, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a, "tree"_a, "need_grad_input"_a = true);
     cuda.def("upsample_const_forward", &upsample_const_forward, "aprs"_a, "input"_a, "level_delta"_a);
     cuda.def("upsample_const_backward", &upsample_const_backward, "aprs"_a, "grad_output"_a, "level_delta"_a);
     cuda.def("restrict_kernel333_forward", &restrict_kernel_333_forward, "weights"_a, "num_levels"_a);

@@ -989,14 +989,14 @@ extern "C" int aprnet_conv333_forward_tc(aprnet_apr* a, int dl, int cin, int cou
 }
 
 // Complete backward pass of the 3x3x3 convolution with the contractions on the tensor cores:
-// grad_weights (accumulated into), grad_input (written; float32 (Cin, ld_in)).
+// grad_weights (accumulated into), grad_input (written; float32 (Cin, ld_in); may be null: skipped).
 //   tree means -> packed input rows, packed dO rows -> weight gradient (tcgen05, deterministic)
 //   -> same-level input gradient (tcgen05 gather) -> cross-level part (atomicAdd) + tree adjoint.
 extern "C" int aprnet_conv333_backward_tc(aprnet_apr* a, int dl, int cin, int cout, int slots, const float* in, int64_t ld_in,
                                           const float* gout, int64_t ld_out, const float* w, float* gin, float* gw,
                                           float* tree, int tree_valid, float* gtree, int64_t ld_tree, float* partial,
                                           void* workspace, void* stream) {
-    APRNET_ARG_CHECK(a && a->valid_dl(dl) && cin > 0 && cout > 0 && slots > 0 && in && gout && w && gin && gw && tree && gtree && partial && workspace, "bad argument");
+    APRNET_ARG_CHECK(a && a->valid_dl(dl) && cin > 0 && cout > 0 && slots > 0 && in && gout && w && gw && tree && gtree && partial && workspace, "bad argument");
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl) && ld_tree >= a->tree_size(dl), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
     int rc = tree_valid ? APRNET_OK : aprnet_fill_tree_mean_forward(a, dl, APRNET_F32, cin, in, ld_in, tree, ld_tree, st);
@@ -1010,6 +1010,7 @@ extern "C" int aprnet_conv333_backward_tc(aprnet_apr* a, int dl, int cin, int co
     if ((rc = aprnet_tc_pack_rows(in, ld_in, n, tree, ld_tree, t, cin, xpad, xrows, st))) return rc;
     if ((rc = aprnet_tc_pack_rows(gout, ld_out, n, nullptr, 0, 0, cout, gpad, grows, st))) return rc;
     if ((rc = aprnet_conv333_backward_weights_tc(a, dl, cin, cout, slots, xrows, xpad, grows, gpad, gw, partial, st))) return rc;
+    if (!gin) return APRNET_OK;          // the caller does not need the input gradient (first layer of a network)
     if ((rc = aprnet_tc_gather_conv(a, dl, 1, cin, cout, slots, grows, gpad, n, n, w, wp, gin, ld_in, st))) return rc;
     void* edge_ws = (char*) wp + aprnet_tc_weight_bytes(cout, cin, slots);
     return aprnet_conv333_backward_input_cross_level_tc(a, dl, cin, cout, slots, grows, gpad, w, gin, ld_in, gtree, ld_tree, wp, edge_ws,

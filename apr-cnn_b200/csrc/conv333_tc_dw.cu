@@ -3,94 +3,32 @@
 //
 //     dW[tap][ci][co] = sum over output locations p of  X[nbr(tap, p)][ci] * dO[p][co]
 //
-// is a GEMM whose contraction index is the particle.  Per block: a contiguous range of locations of
-// one level, one block of KCI input channels and one block of NCO output channels.  The accumulator
-// D[(tap, ci)][co] lives in TMEM for the whole range: 128-row tiles of 128/KCI taps x KCI channels,
-// ceil(27 / (128/KCI)) tiles side by side, NCO fp32 columns each (<= 448 of the 512 columns).  Both
-// operands are MN-major: the gathered neighbour rows of a tap ([8-channel chunk][particle][8]) are the
-// A operand with M = channels and K = particles as they lie in shared memory after the 16-byte
-// cp.async row copies, and the dO rows are the B operand in the same arrangement.  Each block writes
-// its partial sums once; a second pass adds the ranges in ascending order (no atomics).
+// is a GEMM whose contraction index is the particle.  One block owns a contiguous range of locations of
+// one level, a group of taps, a block of CIB input channels and up to 256 output channels.  Its
+// accumulators D[(tap, ci)][co] stay in TMEM for the whole range: 128-row tiles of 128 / CIB taps x CIB
+// channels, NCOL fp32 columns each, side by side in the 512 columns; the tap group is as large as the
+// columns allow, so the gathered rows are read once (CIB = all channels) and only the small dO rows are
+// re-read per tap group.  Both operands are MN-major with the 128-byte hardware swizzle: a gathered
+// neighbour row piece (CIB channels) and a dO row are contiguous in shared memory as they are in global
+// memory, with K = particles.  Warp roles: 8 producer warps (two stages in issue at once, four warps of
+// 32 particles each per stage; table entries are loaded by the lane that owns the particle, one stage
+// ahead, and passed between lanes by shuffles; arrival on the stage barrier is asynchronous), one MMA
+// thread, epilogue by warps 0-3 after the last MMA.  Each block writes its partial sums once; a second
+// pass adds the ranges in ascending order (no atomics).
 // Reference arithmetic: pyapr/aprnet/src/helpers.hpp:624-702 (accumulate_convolution_backward, dW part).
 #include "apr_device.cuh"
+#include "tc_ptx.cuh"
 #include <cuda_bf16.h>
 #include <algorithm>
 
 namespace {
 
+using namespace tcptx;
 typedef long long ll;
-constexpr int PT = 128;            // particles per staged chunk (= threads per block)
-constexpr int XS = 4;              // ring of gathered-row stages
-constexpr int XAHEAD = 2;          // stages of copies in flight (ring slots are refilled two MMA steps after they were read)
-constexpr unsigned SPIN_LIMIT = 1u << 22;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-#ifdef APRNET_TC_CG
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
-#else
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
-#endif
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template<int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                 "selp.b32 %0, 1, 0, p;\n\t}\n" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (unsigned it = 0; it < SPIN_LIMIT; ++it)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_dst), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "setp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-
-// MN-major, no swizzle: core matrix = 8 K-rows x 16 bytes (8 M/N elements); consecutive K rows are
-// 16 bytes apart; LBO = byte distance between groups of 8 K rows, SBO = between 8-element M/N chunks.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-    return (uint64_t) ((saddr >> 4) & 0x3FFF) | ((uint64_t) ((lbo >> 4) & 0x3FFF) << 16) |
-           ((uint64_t) ((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46);
-}
-// D fp32, A/B bf16, both MN-major, M = 128, N = n
-__host__ __device__ constexpr uint32_t make_idesc_mn(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (128 >> 4) << 24);
-}
+constexpr int PT = 128;                       // particles per stage (K extent of one stage)
+constexpr int DW_THREADS = 9 * 32;            // 8 producer warps + 1 MMA warp
+constexpr int DW_MAX_STAGES = 6;
+constexpr int A_STAGE = 2 * PT * 128;         // 128 accumulator rows = two 64-element swizzle atoms per particle
 
 struct DwParams {
     ll seg_begin, seg_end, range_len;      // output locations [seg_begin, seg_end) split into ranges of range_len
@@ -100,168 +38,193 @@ struct DwParams {
     const __nv_bfloat16* grows; int gpad;  // packed dO [N + 1][gpad], zeros at row g_zero_row
     ll g_zero_row;
     float* partial;                        // [range][cout][cin][27]
-    int cin, cout, ci_blocks;
+    int cin, cout, ci_blocks, groups, taps_per_group;
     int* error_flag;
 };
 
-template<int KCI, int NCO>
-__global__ void __launch_bounds__(PT) conv333_tc_dw_kernel(const DwParams P) {
-    constexpr int TPM = 128 / KCI;                      // taps per 128-row accumulator tile
-    constexpr int MT = (27 + TPM - 1) / TPM;            // accumulator tiles
-    constexpr int XCH = KCI / 8;                        // 16-byte chunks per gathered row
-    constexpr int X_BYTES = 128 * PT * 2;               // one stage: TPM taps x KCI channels x PT particles
-    constexpr int G_BYTES = NCO * PT * 2;
-    constexpr int NEED_COLS = MT * NCO + (NCO < 32 ? 32 - NCO : 0);     // accumulators are read back 32 columns at a time
-    constexpr int TMEM_COLS = (NEED_COLS <= 32) ? 32 : (NEED_COLS <= 64) ? 64 : (NEED_COLS <= 128) ? 128 : (NEED_COLS <= 256) ? 256 : 512;
-    static_assert(NEED_COLS <= 512, "accumulators must fit the 512 TMEM columns");
-    constexpr uint32_t IDESC = make_idesc_mn(NCO);
+template<int CIB, int NCOL>
+__global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwParams P, const int nstage) {
+    constexpr int TPT = 128 / CIB;                      // taps per 128-row accumulator tile
+    constexpr int PC = CIB / 8;                         // 16-byte chunks per gathered row piece
+    constexpr int G_BYTES = (NCOL / 64) * PT * 128;     // one dO chunk: NCOL / 64 swizzle atoms per particle
+    constexpr uint32_t IDESC = make_idesc(NCOL, true, true);
+    constexpr uint32_t ATOM_STRIDE = PT * 128;          // between 64-element atoms along M (or N)
 
-    extern __shared__ __align__(128) unsigned char smem[];
-    unsigned char* xs = smem;                                                   // XS * X_BYTES
-    unsigned char* gs = xs + XS * X_BYTES;                                      // 2 * G_BYTES
-    int32_t* idx_s = reinterpret_cast<int32_t*>(gs + 2 * G_BYTES);             // 2 x [27][PT] source rows (by chunk parity)
-    uint64_t* bars = reinterpret_cast<uint64_t*>(idx_s + 2 * 27 * PT);         // XS + 1
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + XS + 1);
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned char* a_ring = smem;                                               // nstage * A_STAGE
+    unsigned char* g_ring = a_ring + (size_t) nstage * A_STAGE;                 // 2 * G_BYTES
+    uint64_t* bars = reinterpret_cast<uint64_t*>(g_ring + 2 * G_BYTES);
+    uint64_t* full = bars;                       // [nstage] gathered rows landed (4 warps x 32 lanes)
+    uint64_t* empty = bars + DW_MAX_STAGES;      // [nstage] MMAs that read the stage completed
+    uint64_t* dfull = empty + DW_MAX_STAGES;     // [2] dO chunk landed
+    uint64_t* dempty = dfull + 2;                // [2] MMAs that read the dO chunk completed
+    uint64_t* done = dempty + 2;                 // all MMAs of the range completed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int cib = blockIdx.y % P.ci_blocks, cob = blockIdx.y / P.ci_blocks;
+    const int grp = blockIdx.y % P.groups, cib = (blockIdx.y / P.groups) % P.ci_blocks, cob = blockIdx.y / (P.groups * P.ci_blocks);
+    const int tap0 = grp * P.taps_per_group;
+    const int ntaps = min(P.taps_per_group, 27 - tap0);
+    const int MT = (ntaps + TPT - 1) / TPT;             // accumulator tiles of this block
     const ll pb = P.seg_begin + (ll) blockIdx.x * P.range_len;
     const ll pe = min(P.seg_end, pb + P.range_len);
     const int nchunks = pe > pb ? (int) ((pe - pb + PT - 1) / PT) : 0;
-    const int nstages = nchunks * MT;
+    const int total_stages = nchunks * MT;
+    const int gpiece = min(256, P.gpad - cob * 256);    // dO channels of this block
 
+    // dO columns beyond gpiece are never copied: they must read as zeros
+    for (int e = tid; e < 2 * G_BYTES / 16; e += DW_THREADS) reinterpret_cast<uint4*>(g_ring)[e] = make_uint4(0, 0, 0, 0);
+    fence_proxy_async();
     if (tid == 0) {
-        for (int i = 0; i <= XS; ++i) mbar_init(smem_u32(bars + i), 1);
+        for (int i = 0; i < nstage; ++i) { mbar_init(smem_u32(full + i), 128); mbar_init(smem_u32(empty + i), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(dfull + i), 128); mbar_init(smem_u32(dempty + i), 1); }
+        mbar_init(smem_u32(done), 1);
+        *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+    if (warp == 8) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_d = *tmem_slot;
+    bool failed = false;
 
-    auto load_idx = [&](int chunk) {          // source rows of this thread's particle for all taps
-        const ll p = pb + (ll) chunk * PT + tid;
-        int32_t* dst = idx_s + (chunk & 1) * 27 * PT;
-        int32_t q[27];          // one batch of independent loads, then the dependent stores
+    if (warp < 8 && total_stages > 0) {
+        // ---------------- producers ----------------
+        const int gq = warp >> 2, wq = warp & 3;        // stage parity handled / 32-particle quarter of the stage
+        const int c = lane % PC, r0 = lane / PC;
+        constexpr int RPI = 32 / PC;                    // particles covered by one copy instruction
+        int32_t rows_cur[TPT], rows_nxt[TPT];
+        auto load_rows = [&](int s, int32_t (&rows)[TPT]) {      // source rows of this lane's particle for the taps of stage s
+            const int chunk = s / MT, mt = s - chunk * MT;
+            const ll p = pb + (ll) chunk * PT + wq * 32 + lane;
 #pragma unroll
-        for (int tap = 0; tap < 27; ++tap) q[tap] = (p < pe) ? __ldg(P.nbr + (ll) tap * P.N + p) : APRNET_NONE;
+            for (int tl = 0; tl < TPT; ++tl) {
+                const int t = mt * TPT + tl;
+                ll r = P.zero_row;
+                if (p < pe && t < ntaps) {
+                    const int32_t v = __ldg(P.nbr + (ll) (tap0 + t) * P.N + p);
+                    if (v >= 0) r = v; else if (v != APRNET_NONE) r = P.tree_base + aprnet_dec_tree(v);
+                }
+                rows[tl] = (int32_t) r;
+            }
+        };
+        int s = gq;
+        if (s < total_stages) load_rows(s, rows_cur);
+        while (s < total_stages) {
+            const int s_nxt = s + 2;
+            if (s_nxt < total_stages) load_rows(s_nxt, rows_nxt);      // in flight while this stage is issued
+            const int chunk = s / MT, mt = s - chunk * MT;
+            const uint32_t slot = (uint32_t) s % (uint32_t) nstage, use = (uint32_t) s / (uint32_t) nstage;
+            if (use > 0 && !mbar_wait_warp(smem_u32(empty + slot), (use - 1) & 1, abort_flag)) { failed = true; break; }
+            if (mt == 0) {
+                // this warp's 32 rows of the dO chunk
+                const uint32_t db = chunk & 1, duse = chunk >> 1;
+                if (duse > 0 && !mbar_wait_warp(smem_u32(dempty + db), (duse - 1) & 1, abort_flag)) { failed = true; break; }
+                unsigned char* g_s = g_ring + db * G_BYTES;
+                const int gc = gpiece / 8;
+                for (int e = lane; e < 32 * gc; e += 32) {
+                    const int pl = e / gc, cc = e - pl * gc, k = wq * 32 + pl;
+                    const ll p = pb + (ll) chunk * PT + k;
+                    cp_async16(smem_u32(g_s + (cc >> 3) * ATOM_STRIDE + k * 128 + (((cc & 7) ^ (k & 7)) << 4)),
+                               P.grows + (p < pe ? p : P.g_zero_row) * P.gpad + cob * 256 + cc * 8);
+                }
+                cp_async_arrive_noinc(smem_u32(dfull + db));
+            }
+            unsigned char* a_s = a_ring + (size_t) slot * A_STAGE;
+            const __nv_bfloat16* src0 = P.xrows + cib * CIB + c * 8;
 #pragma unroll
-        for (int tap = 0; tap < 27; ++tap) {
-            ll r = P.zero_row;
-            if (q[tap] >= 0) r = q[tap]; else if (q[tap] != APRNET_NONE) r = P.tree_base + aprnet_dec_tree(q[tap]);
-            dst[tap * PT + tid] = (int32_t) r;
-        }
-    };
-    auto issue_loads = [&](int stage) {
-        const int chunk = stage / MT, mt = stage % MT;
-        unsigned char* x_s = xs + (stage % XS) * X_BYTES;
-        const int32_t* idx = idx_s + (chunk & 1) * 27 * PT;
-        // lanes sweep the 16-byte chunks of a row first: a warp instruction reads whole rows
-        {
-            const int j = tid % XCH, r0 = tid / XCH;
+            for (int tl = 0; tl < TPT; ++tl) {
+                const int m = tl * CIB + c * 8;                        // accumulator row of this chunk's first channel
+                const uint32_t dst0 = smem_u32(a_s + (m >> 6) * ATOM_STRIDE);
+                const int cc = (m & 63) >> 3;
 #pragma unroll
-            for (int t = 0; t < TPM; ++t) {
-                const int tap = mt * TPM + t;
-#pragma unroll
-                for (int i = 0; i < XCH; ++i) {
-                    const int p = i * (PT / XCH) + r0;
-                    const ll r = tap < 27 ? (ll) idx[tap * PT + p] : P.zero_row;
-                    cp_async16(smem_u32(x_s + ((t * XCH + j) * PT + p) * 16), P.xrows + r * P.xpad + cib * KCI + j * 8);
+                for (int pi = 0; pi < PC; ++pi) {
+                    const int pl = pi * RPI + r0;
+                    const int32_t r = __shfl_sync(0xffffffffu, rows_cur[tl], pl);
+                    const int k = wq * 32 + pl;
+                    cp_async16(dst0 + k * 128 + ((cc ^ (k & 7)) << 4), src0 + (ll) r * P.xpad);
                 }
             }
-        }
-        if (mt == 0) {
-            constexpr int GCH = NCO / 8;
-            unsigned char* g_s = gs + (chunk & 1) * G_BYTES;
-            const int j = tid % GCH, r0 = tid / GCH;
+            // the stage's barrier receives this thread's arrival when the copies above have landed
+            cp_async_arrive_noinc(smem_u32(full + slot));
 #pragma unroll
-            for (int i = 0; i < GCH; ++i) {
-                const int pl = i * (PT / GCH) + r0;
-                const ll p = pb + (ll) chunk * PT + pl;
-                cp_async16(smem_u32(g_s + (j * PT + pl) * 16), P.grows + (p < pe ? p : P.g_zero_row) * P.gpad + cob * NCO + j * 8);
-            }
-        }
-    };
-
-    bool failed = false;
-    if (nchunks > 0) load_idx(0);
-    __syncthreads();
-    for (int s = 0; s < XAHEAD; ++s) {
-        if (s < nstages) {
-            issue_loads(s);
+            for (int tl = 0; tl < TPT; ++tl) rows_cur[tl] = rows_nxt[tl];
+            s = s_nxt;
         }
         cp_async_commit();
+        cp_async_wait<0>();
+    } else if (warp == 8 && total_stages > 0) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            uint32_t slot = 0, use = 0;
+            for (int chunk = 0; chunk < nchunks && !failed; ++chunk) {
+                const uint32_t db = chunk & 1, duse = chunk >> 1;
+                const uint32_t b_addr = smem_u32(g_ring + db * G_BYTES);
+                for (int mt = 0; mt < MT; ++mt) {
+                    if (!mbar_wait(smem_u32(full + slot), use & 1, abort_flag)) { failed = true; break; }
+                    if (mt == 0 && !mbar_wait(smem_u32(dfull + db), duse & 1, abort_flag)) { failed = true; break; }
+                    fence_proxy_async();          // generic-proxy writes of the cp.async copies -> tensor-core (async proxy) reads
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(a_ring + (size_t) slot * A_STAGE);
+#pragma unroll
+                    for (int k = 0; k < PT / 16; ++k) {
+                        // 16 particles = two 8-row groups of 1024 bytes; atoms along M / N are ATOM_STRIDE apart
+                        const uint64_t da = make_desc(a_addr + k * 2048, ATOM_STRIDE, 1024, 2);
+                        const uint64_t dbd = make_desc(b_addr + k * 2048, ATOM_STRIDE, 1024, 2);
+                        umma_bf16(tmem_d + mt * NCOL, da, dbd, IDESC, (chunk > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(empty + slot));
+                    if (mt == MT - 1) umma_commit(smem_u32(dempty + db));
+                    if (++slot == (uint32_t) nstage) { slot = 0; ++use; }
+                }
+            }
+            if (!failed) umma_commit(smem_u32(done));
+        }
     }
-    for (int stage = 0; stage < nstages; ++stage) {
-        const int chunk = stage / MT, mt = stage % MT;
-        cp_async_wait<XAHEAD - 1>();
-        fence_proxy_async();
-        if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }
-        if (mt == 0 && chunk + 1 < nchunks) load_idx(chunk + 1);      // read by other threads from stage (chunk, MT - XAHEAD) on, after further barriers
-        if (tid == 0) {
+
+    // ---------------- epilogue: warps 0-3 ----------------
+    float* dst = P.partial + (ll) blockIdx.x * P.cout * P.cin * 27;
+    if (warp < 4 && total_stages > 0 && !failed) {
+        if (!mbar_wait_warp(smem_u32(done), 0, abort_flag)) failed = true;
+        if (!failed) {
             tc_fence_after();
-            const uint32_t a_addr = smem_u32(xs + (stage % XS) * X_BYTES);
-            const uint32_t b_addr = smem_u32(gs + (chunk & 1) * G_BYTES);
+            const int row = warp * 32 + lane;                 // accumulator row = (tap within tile) * CIB + ci
+            const int tl = row / CIB, ci = cib * CIB + row % CIB;
+            for (int mt = 0; mt < MT; ++mt) {
+                const int t = mt * TPT + tl;
 #pragma unroll
-            for (int k = 0; k < PT / 16; ++k) {
-                const uint64_t da = make_desc(a_addr + k * 256, 128, PT * 16);
-                const uint64_t db = make_desc(b_addr + k * 256, 128, PT * 16);
-                umma_bf16(tmem_d + mt * NCO, da, db, IDESC, (chunk > 0 || k > 0) ? 1u : 0u);
-            }
-            umma_commit(smem_u32(bars + stage % XS));
-            if (stage == nstages - 1) umma_commit(smem_u32(bars + XS));
-        }
-        const int nxt = stage + XAHEAD;
-        if (nxt < nstages) {
-            if (nxt >= XS) {
-                const uint32_t use = nxt / XS;
-                if (!mbar_wait(smem_u32(bars + nxt % XS), (use - 1) & 1)) failed = true;
-            }
-            if (!failed) issue_loads(nxt);
-        }
-        cp_async_commit();
-    }
-
-    if (nstages > 0 && !failed) {
-        const bool ok = mbar_wait(smem_u32(bars + XS), 0);
-        if (__syncthreads_or(ok ? 0 : 1)) failed = true;
-    }
-    if (!failed && nstages > 0) {
-        tc_fence_after();
-        float* dst = P.partial + (ll) blockIdx.x * P.cout * P.cin * 27;
-        const int row = warp * 32 + lane;                 // accumulator row = (tap within tile) * KCI + ci
-        const int t_in = row / KCI, ci = cib * KCI + row % KCI;
+                for (int c0 = 0; c0 < NCOL; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_d + ((uint32_t) (warp * 32) << 16) + mt * NCOL + c0, r);
+                    tmem_ld_wait();
+                    if (t < ntaps && ci < P.cin) {
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            const int tap = mt * TPM + t_in;
-#pragma unroll
-            for (int c0 = 0; c0 < NCO; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_d + ((uint32_t) (warp * 32) << 16) + mt * NCO + c0, r);
-                tmem_ld_wait();
-                if (tap < 27 && ci < P.cin) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int co = cob * NCO + c0 + j;
-                        if (c0 + j < NCO && co < P.cout) dst[((ll) co * P.cin + ci) * 27 + tap] = __uint_as_float(r[j]);
+                        for (int j = 0; j < 32; ++j) {
+                            const int co = cob * 256 + c0 + j;
+                            if (co < P.cout) dst[((ll) co * P.cin + ci) * 27 + tap0 + t] = __uint_as_float(r[j]);
+                        }
                     }
                 }
             }
         }
-    } else if (!failed) {
+    } else if (total_stages == 0) {
         // empty range: this block still owns its slice of the partial buffer
-        float* dst = P.partial + (ll) blockIdx.x * P.cout * P.cin * 27;
-        for (int e = tid; e < KCI * NCO * 27; e += PT) {
-            const int tap = e % 27, ci = cib * KCI + (e / 27) % KCI, co = cob * NCO + e / (27 * KCI);
-            if (ci < P.cin && co < P.cout) dst[((ll) co * P.cin + ci) * 27 + tap] = 0.f;
+        for (int e = tid; e < CIB * 256 * ntaps; e += DW_THREADS) {
+            const int t = e % ntaps, ci = cib * CIB + (e / ntaps) % CIB, co = cob * 256 + e / (ntaps * CIB);
+            if (ci < P.cin && co < P.cout) dst[((ll) co * P.cin + ci) * 27 + tap0 + t] = 0.f;
         }
     }
-    cp_async_wait<0>();
-    if (failed && P.error_flag) *P.error_flag = 1;
+
+    if (failed) {
+        *abort_flag = 1;
+        if (P.error_flag) *P.error_flag = 1;
+    }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem_d, TMEM_COLS);
+    if (warp == 8) tmem_dealloc(tmem_d, 512);
 }
 
 template<typename T>
@@ -273,16 +236,18 @@ __global__ void reduce_partial_kernel(const T* __restrict__ partial, int nchunks
     dst[e] += s;
 }
 
-template<int KCI, int NCO>
+template<int CIB, int NCOL>
 int launch_dw(const DwParams& P, int nranges, int blocks_y, cudaStream_t st, const char* pname) {
-    constexpr int MT = (27 + 128 / KCI - 1) / (128 / KCI);
-    (void) MT;
-    const size_t smem = (size_t) XS * 128 * PT * 2 + 2 * (size_t) NCO * PT * 2 + 2 * 27 * PT * 4 + (XS + 1) * 8 + 16;
-    auto kern = conv333_tc_dw_kernel<KCI, NCO>;
+    constexpr size_t G_BYTES = (size_t) (NCOL / 64) * PT * 128;
+    const size_t fixed = 2 * G_BYTES + (2 * DW_MAX_STAGES + 5) * 8 + 16 + 1024;
+    const int nstage = (int) std::min<size_t>(DW_MAX_STAGES, (227 * 1024 - 1024 - fixed) / A_STAGE);
+    if (nstage < 2) { aprnet_set_error("conv333 tensor-core weight gradient: tile does not fit shared memory"); return APRNET_ERR_UNSUPPORTED; }
+    const size_t smem = (size_t) nstage * A_STAGE + fixed;
+    auto kern = conv333_tc_dw_kernel<CIB, NCOL>;
     APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     dim3 grid((unsigned) nranges, (unsigned) blocks_y);
     { AprnetProfScope _prof(pname, st);
-    kern<<<grid, PT, smem, st>>>(P);
+    kern<<<grid, DW_THREADS, smem, st>>>(P, nstage);
     }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
@@ -307,9 +272,16 @@ extern "C" int aprnet_conv333_backward_weights_tc(aprnet_apr* a, int dl, int cin
     const AprPlan* plan = aprnet_get_plan(a, dl, st);
     if (!plan) return APRNET_ERR_CUDA;
     const ll n = plan->n, t = plan->tree_size;
-    const int kci = (xpad % 32 == 0) ? 32 : 16;
-    const int nco = (gpad % 64 == 0) ? 64 : ((gpad % 32 == 0) ? 32 : 16);
-    const int ci_blocks = xpad / kci, co_blocks = gpad / nco;
+    // input-channel block: the widest of 128 / 64 / 32 / 16 that divides the padded width (gathered once when it covers all channels)
+    const int cibk = (xpad % 128 == 0) ? 128 : ((xpad % 64 == 0) ? 64 : ((xpad % 32 == 0) ? 32 : 16));
+    const int ci_blocks = xpad / cibk;
+    const int co_blocks = (gpad + 255) / 256;
+    const int ncol = (std::min(gpad, 256) + 63) / 64 * 64;                 // accumulator columns per tile
+    const int tpt = 128 / cibk;
+    const int max_taps = (512 / ncol) * tpt;                               // taps whose accumulators fit the 512 TMEM columns
+    const int groups = (27 + max_taps - 1) / max_taps;
+    const int taps_per_group = ((27 + groups - 1) / groups + tpt - 1) / tpt * tpt;
+    const int blocks_y = groups * ci_blocks * co_blocks;
     const ll elems = (ll) 27 * cin * cout;
     const ll max_ranges = aprnet_conv333_tc_dw_partial_elems(cin, cout) / elems;
     int dev = 0, sms = 148;
@@ -319,8 +291,8 @@ extern "C" int aprnet_conv333_backward_weights_tc(aprnet_apr* a, int dl, int cin
     snprintf(pname, sizeof(pname), "conv333_tc_dw:ci%d:co%d:dl%d", cin, cout, dl);
     for (const Segment& s : aprnet_segments(a, dl, slots, false)) {
         const ll len = s.end - s.begin;
-        // enough ranges to fill the GPU a few times over, each at least 4 chunks long
-        ll want = std::max<ll>(1, (ll) 3 * sms / std::max(1, ci_blocks * co_blocks));
+        // one block per SM at a time: enough ranges for two waves, each at least 4 chunks long
+        ll want = std::max<ll>(1, ((ll) 2 * sms + blocks_y - 1) / blocks_y);
         want = std::min<ll>(want, (len + 4 * PT - 1) / (4 * PT));
         const int nranges = (int) std::max<ll>(1, std::min<ll>(max_ranges, want));
         DwParams P;
@@ -329,11 +301,14 @@ extern "C" int aprnet_conv333_backward_weights_tc(aprnet_apr* a, int dl, int cin
         P.nbr = plan->nbr; P.N = n;
         P.xrows = (const __nv_bfloat16*) xrows; P.xpad = xpad; P.tree_base = n; P.zero_row = n + t;
         P.grows = (const __nv_bfloat16*) grows; P.gpad = gpad; P.g_zero_row = n;
-        P.partial = partial; P.cin = cin; P.cout = cout; P.ci_blocks = ci_blocks;
+        P.partial = partial; P.cin = cin; P.cout = cout; P.ci_blocks = ci_blocks; P.groups = groups; P.taps_per_group = taps_per_group;
         P.error_flag = aprnet_tc_error_flag_device();
         int rc;
-#define DW_CASE(KCI_, NCO_) if (kci == KCI_ && nco == NCO_) rc = launch_dw<KCI_, NCO_>(P, nranges, ci_blocks * co_blocks, st, pname); else
-        DW_CASE(32, 64) DW_CASE(32, 32) DW_CASE(32, 16) DW_CASE(16, 64) DW_CASE(16, 32) DW_CASE(16, 16)
+#define DW_CASE(CIB_, NCOL_) if (cibk == CIB_ && ncol == NCOL_) rc = launch_dw<CIB_, NCOL_>(P, nranges, blocks_y, st, pname); else
+        DW_CASE(16, 64) DW_CASE(16, 128) DW_CASE(16, 192) DW_CASE(16, 256)
+        DW_CASE(32, 64) DW_CASE(32, 128) DW_CASE(32, 192) DW_CASE(32, 256)
+        DW_CASE(64, 64) DW_CASE(64, 128) DW_CASE(64, 192) DW_CASE(64, 256)
+        DW_CASE(128, 64) DW_CASE(128, 128) DW_CASE(128, 192) DW_CASE(128, 256)
         { aprnet_set_error("conv333 tensor-core weight gradient: unsupported blocking"); return APRNET_ERR_UNSUPPORTED; }
 #undef DW_CASE
         if (rc) return rc;

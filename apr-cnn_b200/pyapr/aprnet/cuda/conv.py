@@ -37,7 +37,9 @@ class Conv333Function(Function):
     def backward(ctx, grad_output):
         inputs, expanded, bias, level_deltas, tree = ctx.saved_tensors
         grad_output = grad_output.contiguous()
-        grad_input, grad_expanded = conv333_backward_with_tree(APRPtrVector(ctx.aprs), inputs, expanded, grad_output, level_deltas, tree)
+        # the input gradient of a first layer (features that do not require grad) is not computed
+        grad_input, grad_expanded = conv333_backward_with_tree(APRPtrVector(ctx.aprs), inputs, expanded, grad_output, level_deltas, tree,
+                                                               bool(ctx.needs_input_grad[0]))
         grad_weights = restrict_kernel333_backward(grad_expanded, ctx.num_stencils)
         grad_bias = grad_output.sum(dim=(0, 2)) if bias is not None else None
         return grad_input, grad_weights, grad_bias, None, None

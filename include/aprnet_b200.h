@@ -140,9 +140,9 @@ int aprnet_conv333_forward_tc(aprnet_apr* apr, int level_delta, int cin, int cou
                               float* tree_scratch, int64_t ld_tree, void* workspace, void* stream);
 /* Complete backward pass with the contractions on the tensor cores.  grad_weights
  * (num_slots, Cout, Cin, 27) is accumulated into (deterministic block partials + fixed-order second
- * pass); grad_input (Cin, ld_in) is written.  Steps: tree means of the input -> bf16 channels-last
+ * pass); grad_input (Cin, ld_in) is written (pass NULL to skip the input gradient).  Steps: tree means of the input -> bf16 channels-last
  * copies of input and grad_output -> weight gradient -> same-level part of the input gradient (a
- * gather) -> cross-level part (atomicAdd onto coarser particles / tree nodes) and tree adjoint.
+ * gather) -> cross-level part (edge-list GEMM + deterministic per-target sums) and tree adjoint.
  * tree / grad_tree: (Cin, ld_tree) float scratch (pass tree_scratch_is_valid = 1 when tree_scratch still
  * holds the tree means that the forward call left there: the fill is then skipped); partial: aprnet_conv333_tc_dw_partial_elems()
  * floats; workspace: aprnet_conv333_tc_workspace_bytes() bytes. */
