@@ -37,20 +37,24 @@ struct AprPlan {                 // cached per level_delta
     int32_t* nbr = nullptr;      // [27][n]
 };
 
-// Cross-level edges of one level_delta: every (output location p, tap) whose source is a coarser
-// particle or a tree node.  Edges are numbered tap-major, then by p; `src[e]` = p; the edges that end
-// at one target are listed (ascending) in tgt_edge[tgt_ptr[t] .. tgt_ptr[t+1]), targets numbered as
-// particle index, or N + tree index.
-struct EdgeGroup { long long begin, end; int tap, level; };
+// Cross-level edges of one level_delta: every (output location p, tap) whose source ("target" of the
+// gradient) is a coarser particle or a tree node.  Targets are numbered as particle index, or
+// N + tree index.  The edges of one (target, tap) form a "virtual row": their dO rows are summed before
+// the contraction, because they all meet the same weight matrix.  Virtual rows are numbered by
+// ascending target, then tap; vsrc[vstart[v] .. vstart[v + 1]) lists the locations p of row v in
+// ascending order.  active[] lists the targets that have at least one edge (ascending), vnbr[tap][a] is
+// the virtual row of (active[a], tap) or -1.
+struct ActiveSeg { long long begin, end; int location_level; };     // range of active[] whose edges come from one level
 struct EdgePlan {
-    long long n_edges = 0, n_targets = 0, n_active = 0;
-    int32_t* src = nullptr;        // [n_edges]
-    int32_t* tgt_ptr = nullptr;    // [n_targets + 1]
-    int32_t* tgt_edge = nullptr;   // [n_edges]
-    int32_t* active = nullptr;     // [n_active] targets with at least one edge
-    void* groups_dev = nullptr;    // device copy of the tile table (rebuilt when the slot count changes)
-    int groups_slots = -1;
-    std::vector<EdgeGroup> groups; // non-empty (tap, level) ranges in edge order
+    long long n_edges = 0, n_targets = 0, n_active = 0, n_vrows = 0;
+    int32_t* vsrc = nullptr;       // [n_edges]
+    int32_t* vstart = nullptr;     // [n_vrows + 1]
+    int32_t* active = nullptr;     // [n_active]
+    int32_t* vnbr = nullptr;       // [27][n_active]
+    std::vector<ActiveSeg> segs;   // by level, in active[] order
+    // coarse map for splitting the work when the virtual rows do not fit the workspace: chunk k starts at
+    // active index chunk_a[k] and virtual row chunk_v[k]; chunks hold about VROW_GRANULE rows
+    std::vector<long long> chunk_a, chunk_v;
 };
 
 struct aprnet_apr {
@@ -126,14 +130,16 @@ extern "C" int aprnet_conv333_backward_input_cross_level(aprnet_apr* a, int dl, 
 
 EdgePlan* aprnet_get_edge_plan(aprnet_apr* apr, int dl, cudaStream_t stream);
 void aprnet_free_edge_plan(EdgePlan& ep);
-// edge-list GEMM: rows_out[e - e0][0..row_pad) = packed dO row src[e] times W[slot][:, :, tap]^T, for the edges of groups [g0, g1)
-int aprnet_tc_edge_gemm(aprnet_apr* a, int dl, int cin, int cout, int slots, const void* grows, int gpad, long long zero_row,
-                        const void* wp_packed, EdgePlan* ep, int g0, int g1, float* rows_out, int row_pad, cudaStream_t st);
+// gather GEMM over the active targets [a0, a1) of an edge plan: grad[target] += sum over taps of
+// W[slot][:, :, tap]^T times virtual row vnbr[tap][a] (rows: bf16 [.. ][gpad], row index relative to `vrows`)
+int aprnet_tc_gather_targets(aprnet_apr* a, int dl, int cin, int cout, int slots, const void* vrows, int gpad, long long zero_row,
+                             const void* wp_packed, const EdgePlan* ep, long long a0, long long a1,
+                             float* gin, long long ld_in, float* gtree, long long ld_tree, cudaStream_t st);
 int aprnet_tc_pack_weights(const float* w, int slots, int cin, int cout, int mode, void* wp, cudaStream_t st);
 size_t aprnet_tc_weight_bytes(int k_dim, int n_dim, int slots);
 size_t aprnet_tc_rows_bytes(long long rows, int channels);
 int aprnet_tc_pad(int channels);
-extern "C" int64_t aprnet_edge_workspace_bytes(const aprnet_apr* a, int dl, int cin);
+extern "C" int64_t aprnet_edge_workspace_bytes(const aprnet_apr* a, int dl, int cout);
 extern "C" int aprnet_conv333_backward_input_cross_level_tc(aprnet_apr* a, int dl, int cin, int cout, int slots,
                                                             const void* grows, int gpad, const float* w, float* gin,
                                                             int64_t ld_in, float* gtree, int64_t ld_tree, void* wp_ws,

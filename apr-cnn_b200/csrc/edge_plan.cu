@@ -3,15 +3,15 @@
 // A tap of an output location p whose source is a coarser particle or a tree node ("cross-level edge")
 // contributes W[tap]^T dO[p] to that source.  The reference scatters these with atomicAdd
 // (pyapr/aprnet/cuda/src/conv333_gpu_backward.cu:184-192,417,643).  Here the edges of a level_delta are
-// enumerated once (cached in the APR handle): edge ids run tap-major, then by location, so all edges of
-// one (tap, level) form a contiguous range that shares one weight matrix.  The gradient is then
-//   pass 1: an edge-list GEMM on the tensor cores (rows of dO gathered by edge, times W[tap]^T) that
-//           writes one result row per edge, and
-//   pass 2: a pull: every target sums the rows of its incoming edges in ascending edge order.
-// Both passes are deterministic.  The edge rows go through a bounded workspace, a chunk of whole
-// (tap, level) groups at a time.
+// enumerated once (cached in the APR handle) and grouped by (target, tap): all edges of one group meet
+// the same weight matrix (their locations lie on one level), so their dO rows are summed first
+// ("virtual row", pass 1: a segmented sum in ascending location order) and the contraction becomes an
+// ordinary 27-tap gather GEMM over the targets that have edges (pass 2, on the tensor cores), whose
+// result is added to the gradient of the particle / tree node by exactly one thread.  Both passes are
+// deterministic, and the work is proportional to the number of (target, tap) groups, not edges.
 #include "apr_device.cuh"
 #include <cub/cub.cuh>
+#include <cuda_bf16.h>
 #include <algorithm>
 
 namespace {
@@ -78,41 +78,76 @@ __global__ void edge_compact_active_kernel(const int32_t* __restrict__ pos, ll n
     if (pos[t + 1] != pos[t]) active[pos[t]] = (int32_t) t;
 }
 
-// pass 2: thread = (active target, block of 16 channels); sums the rows of the incoming edges that lie in
-// the current chunk [e0, e1) and adds them to the gradient of the particle / tree node.
-__global__ void edge_pull_kernel(const int32_t* __restrict__ active, ll n_active, const int32_t* __restrict__ ptr,
-                                 const int32_t* __restrict__ tgt_edge, ll e0, ll e1, const float* __restrict__ rows, int row_pad,
-                                 float* __restrict__ gin, ll ld_in, float* __restrict__ gtree, ll ld_tree, ll N, int cin) {
+struct TapBegin { int32_t b[28]; };      // first edge id of every tap (edge ids are tap-major)
+
+// virtual rows of one active target = runs of equal tap in its ascending edge list
+__global__ void vrow_count_kernel(const int32_t* __restrict__ active, ll n_active, const int32_t* __restrict__ ptr,
+                                  const int32_t* __restrict__ tgt_edge, TapBegin tb, int32_t* __restrict__ nruns) {
     const ll a = (ll) blockIdx.x * blockDim.x + threadIdx.x;
-    if (a >= n_active) return;
-    const int t = active[a];
-    int b = ptr[t];
-    const int e = ptr[t + 1];
-    {   // first incoming edge >= e0
-        int hi = e;
-        while (b < hi) { const int m = (b + hi) >> 1; if (tgt_edge[m] < e0) b = m + 1; else hi = m; }
-    }
-    if (b >= e || tgt_edge[b] >= e1) return;
-    const int c0 = blockIdx.y * 16;
-    float acc[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-    for (; b < e; ++b) {
-        const ll ed = tgt_edge[b];
-        if (ed >= e1) break;
-        const float4* r = reinterpret_cast<const float4*>(rows + (ed - e0) * row_pad + c0);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float4 v = r[i];
-            acc[4 * i] += v.x; acc[4 * i + 1] += v.y; acc[4 * i + 2] += v.z; acc[4 * i + 3] += v.w;
+    if (a > n_active) return;
+    int runs = 0;
+    if (a < n_active) {
+        const int t = active[a];
+        int cur = -1, tap = 0;
+        for (int i = ptr[t]; i < ptr[t + 1]; ++i) {
+            const int32_t e = tgt_edge[i];
+            while (e >= tb.b[tap + 1]) ++tap;
+            if (tap != cur) { ++runs; cur = tap; }
         }
     }
-    float* dst = t < N ? gin + t : gtree + (t - N);
-    const ll ld = t < N ? ld_in : ld_tree;
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-        if (c0 + i < cin) dst[(ll) (c0 + i) * ld] += acc[i];
+    nruns[a] = runs;
 }
+
+__global__ void vrow_fill_kernel(const int32_t* __restrict__ active, ll n_active, const int32_t* __restrict__ ptr,
+                                 const int32_t* __restrict__ tgt_edge, const int32_t* __restrict__ src, TapBegin tb,
+                                 const int32_t* __restrict__ vfirst, ll n_edges, int32_t* __restrict__ vstart,
+                                 int32_t* __restrict__ vnbr, int32_t* __restrict__ vsrc) {
+    const ll a = (ll) blockIdx.x * blockDim.x + threadIdx.x;
+    if (a >= n_active) return;
+    if (a == 0) vstart[vfirst[n_active]] = (int32_t) n_edges;
+    const int t = active[a];
+    int cur = -1, tap = 0;
+    int32_t v = vfirst[a] - 1;
+    for (int i = ptr[t]; i < ptr[t + 1]; ++i) {
+        const int32_t e = tgt_edge[i];
+        while (e >= tb.b[tap + 1]) ++tap;
+        if (tap != cur) { cur = tap; ++v; vstart[v] = i; vnbr[(ll) tap * n_active + a] = v; }
+        vsrc[i] = src[e];
+    }
+}
+
+// out[k] = first index i of sorted[0, n) with sorted[i] >= key[k]
+__global__ void lower_bound_kernel(const int32_t* __restrict__ sorted, ll n, const ll* __restrict__ key, int nkeys, ll* __restrict__ out) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= nkeys) return;
+    ll lo = 0, hi = n;
+    while (lo < hi) { const ll m = (lo + hi) >> 1; if ((ll) sorted[m] < key[k]) lo = m + 1; else hi = m; }
+    out[k] = lo;
+}
+
+// pass 1: thread = (virtual row, 8-channel chunk); sums the dO rows of the row's locations in ascending
+// order (fp32) and writes the bf16 row 1 + v - v0 of the workspace (row 0 is the zero row)
+__global__ void vrow_reduce_kernel(const int32_t* __restrict__ vstart, const int32_t* __restrict__ vsrc, ll v0, ll v1,
+                                   const __nv_bfloat16* __restrict__ grows, int gpad, __nv_bfloat16* __restrict__ out) {
+    const int nch = gpad >> 3;
+    const ll e = (ll) blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= (v1 - v0) * nch) return;
+    const ll v = v0 + e / nch;
+    const int c = (int) (e % nch);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int i = vstart[v]; i < vstart[v + 1]; ++i) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(grows + (ll) vsrc[i] * gpad + c * 8));
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { const float2 f = __bfloat1622float2(h[k]); acc[2 * k] += f.x; acc[2 * k + 1] += f.y; }
+    }
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+    *reinterpret_cast<uint4*>(out + (1 + v - v0) * gpad + c * 8) = *reinterpret_cast<const uint4*>(o);
+}
+
+constexpr ll VROW_GRANULE = 4ll << 20;      // virtual rows per entry of the chunk map
 
 template<typename T>
 int dev_alloc(T** p, size_t n, long long* bytes) {
@@ -124,7 +159,7 @@ int dev_alloc(T** p, size_t n, long long* bytes) {
 } // namespace
 
 void aprnet_free_edge_plan(EdgePlan& ep) {
-    cudaFree(ep.src); cudaFree(ep.tgt_ptr); cudaFree(ep.tgt_edge); cudaFree(ep.active); cudaFree(ep.groups_dev);
+    cudaFree(ep.vsrc); cudaFree(ep.vstart); cudaFree(ep.active); cudaFree(ep.vnbr);
     ep = EdgePlan();
 }
 
@@ -137,53 +172,44 @@ static int build_edge_plan(aprnet_apr* a, int dl, const AprPlan* plan, EdgePlan&
     lr.n = (int) segs.size();
     for (int i = 0; i < lr.n; ++i) { lr.begin[i] = segs[i].begin; lr.end[i] = segs[i].end; }
 
-    int32_t *scan = nullptr, *tgt = nullptr, *count = nullptr;
+    // temporaries: flags / scan, per-edge source and target, per-target lists
+    int32_t *scan = nullptr, *src = nullptr, *tgt = nullptr, *count = nullptr, *tgt_ptr = nullptr, *tgt_edge = nullptr, *vfirst = nullptr;
+    ll *keys = nullptr, *found = nullptr;
     void* temp = nullptr;
     int rc = APRNET_OK;
-    auto cleanup = [&]() { cudaFree(scan); cudaFree(tgt); cudaFree(count); cudaFree(temp); };
+    auto cleanup = [&]() { cudaFree(scan); cudaFree(src); cudaFree(tgt); cudaFree(count); cudaFree(tgt_ptr); cudaFree(tgt_edge);
+                           cudaFree(vfirst); cudaFree(keys); cudaFree(found); cudaFree(temp); };
 #define EP_CHECK(expr) do { cudaError_t _e = (expr); if (_e != cudaSuccess) { aprnet_set_error("%s failed: %s", #expr, cudaGetErrorString(_e)); cleanup(); return APRNET_ERR_CUDA; } } while (0)
 
     EP_CHECK(cudaMalloc((void**) &scan, (size_t) (F + 1) * sizeof(int32_t)));
     edge_flag_kernel<<<aprnet_ceil_div(F + 1, 256), 256, 0, st>>>(plan->nbr, N, lr, scan);
     size_t temp_bytes = 0, temp2 = 0;
     EP_CHECK(cub::DeviceScan::ExclusiveSum(nullptr, temp_bytes, scan, scan, (int) (F + 1), st));
-    EP_CHECK(cub::DeviceScan::ExclusiveSum(nullptr, temp2, scan, scan, (int) (NT + 1), st));
+    EP_CHECK(cub::DeviceScan::ExclusiveSum(nullptr, temp2, scan, scan, (int) (NT + 2), st));
     temp_bytes = std::max(temp_bytes, temp2);
     EP_CHECK(cudaMalloc(&temp, std::max<size_t>(temp_bytes, 1)));
     EP_CHECK(cub::DeviceScan::ExclusiveSum(temp, temp_bytes, scan, scan, (int) (F + 1), st));
 
-    // group boundaries: edge id at the start of every (tap, level) range
-    std::vector<int32_t> bounds((size_t) 27 * lr.n * 2);
-    int32_t total = 0;
-    for (int tap = 0; tap < 27; ++tap)
-        for (int i = 0; i < lr.n; ++i) {
-            EP_CHECK(cudaMemcpyAsync(&bounds[(size_t) (tap * lr.n + i) * 2], scan + tap * N + lr.begin[i], sizeof(int32_t), cudaMemcpyDeviceToHost, st));
-            EP_CHECK(cudaMemcpyAsync(&bounds[(size_t) (tap * lr.n + i) * 2 + 1], scan + tap * N + lr.end[i], sizeof(int32_t), cudaMemcpyDeviceToHost, st));
-        }
-    EP_CHECK(cudaMemcpyAsync(&total, scan + F, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+    // first edge id of every tap
+    TapBegin tb;
+    for (int tap = 0; tap <= 27; ++tap)
+        EP_CHECK(cudaMemcpyAsync(&tb.b[tap], scan + (ll) tap * N, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
     EP_CHECK(cudaStreamSynchronize(st));
-    ep.n_edges = total; ep.n_targets = NT;
-    ep.groups.clear();
-    for (int tap = 0; tap < 27; ++tap)
-        for (int i = 0; i < lr.n; ++i) {
-            EdgeGroup g;
-            g.begin = bounds[(size_t) (tap * lr.n + i) * 2]; g.end = bounds[(size_t) (tap * lr.n + i) * 2 + 1];
-            g.tap = tap; g.level = segs[i].level;
-            if (g.end > g.begin) ep.groups.push_back(g);
-        }
+    const ll E = tb.b[27];
+    ep.n_edges = E; ep.n_targets = NT;
 
-    const size_t E = (size_t) total;
-    if ((rc = dev_alloc(&ep.src, E, &a->device_bytes)) || (rc = dev_alloc(&ep.tgt_edge, E, &a->device_bytes)) ||
-        (rc = dev_alloc(&ep.tgt_ptr, (size_t) NT + 1, &a->device_bytes))) { cleanup(); return rc; }
+    // per-edge source and target, per-target ascending edge lists, active targets
+    EP_CHECK(cudaMalloc((void**) &src, std::max<size_t>(E, 1) * sizeof(int32_t)));
     EP_CHECK(cudaMalloc((void**) &tgt, std::max<size_t>(E, 1) * sizeof(int32_t)));
+    EP_CHECK(cudaMalloc((void**) &tgt_edge, std::max<size_t>(E, 1) * sizeof(int32_t)));
+    EP_CHECK(cudaMalloc((void**) &tgt_ptr, (size_t) (NT + 1) * sizeof(int32_t)));
     EP_CHECK(cudaMalloc((void**) &count, (size_t) (NT + 1) * sizeof(int32_t)));
     EP_CHECK(cudaMemsetAsync(count, 0, (size_t) (NT + 1) * sizeof(int32_t), st));
-    edge_emit_kernel<<<aprnet_ceil_div(F, 256), 256, 0, st>>>(plan->nbr, N, scan, ep.src, tgt, count);
-    EP_CHECK(cub::DeviceScan::ExclusiveSum(temp, temp_bytes, count, ep.tgt_ptr, (int) (NT + 1), st));
-    EP_CHECK(cudaMemcpyAsync(count, ep.tgt_ptr, (size_t) (NT + 1) * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));   // cursors
-    if (E) edge_fill_kernel<<<aprnet_ceil_div((ll) E, 256), 256, 0, st>>>(tgt, (ll) E, count, ep.tgt_edge);
-    // sort the lists, flag active targets (flags reuse `count`), compact them
-    edge_sort_kernel<<<aprnet_ceil_div(NT + 1, 128), 128, 0, st>>>(ep.tgt_ptr, NT, ep.tgt_edge, count);
+    edge_emit_kernel<<<aprnet_ceil_div(F, 256), 256, 0, st>>>(plan->nbr, N, scan, src, tgt, count);
+    EP_CHECK(cub::DeviceScan::ExclusiveSum(temp, temp_bytes, count, tgt_ptr, (int) (NT + 1), st));
+    EP_CHECK(cudaMemcpyAsync(count, tgt_ptr, (size_t) (NT + 1) * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));   // cursors
+    if (E) edge_fill_kernel<<<aprnet_ceil_div(E, 256), 256, 0, st>>>(tgt, E, count, tgt_edge);
+    edge_sort_kernel<<<aprnet_ceil_div(NT + 1, 128), 128, 0, st>>>(tgt_ptr, NT, tgt_edge, count);     // also flags active targets in `count`
     EP_CHECK(cub::DeviceScan::ExclusiveSum(temp, temp_bytes, count, count, (int) (NT + 1), st));
     int32_t n_active = 0;
     EP_CHECK(cudaMemcpyAsync(&n_active, count + NT, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
@@ -191,6 +217,68 @@ static int build_edge_plan(aprnet_apr* a, int dl, const AprPlan* plan, EdgePlan&
     ep.n_active = n_active;
     if ((rc = dev_alloc(&ep.active, (size_t) n_active, &a->device_bytes))) { cleanup(); return rc; }
     if (NT) edge_compact_active_kernel<<<aprnet_ceil_div(NT, 256), 256, 0, st>>>(count, NT, ep.active);
+    cudaFree(scan); scan = nullptr;
+    cudaFree(tgt); tgt = nullptr;
+
+    // virtual rows: runs of equal tap in every active target's list
+    EP_CHECK(cudaMalloc((void**) &vfirst, (size_t) (n_active + 1) * sizeof(int32_t)));
+    vrow_count_kernel<<<aprnet_ceil_div((ll) n_active + 1, 128), 128, 0, st>>>(ep.active, n_active, tgt_ptr, tgt_edge, tb, vfirst);
+    EP_CHECK(cub::DeviceScan::ExclusiveSum(temp, temp_bytes, vfirst, vfirst, n_active + 1, st));
+    int32_t n_vrows = 0;
+    EP_CHECK(cudaMemcpyAsync(&n_vrows, vfirst + n_active, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+    EP_CHECK(cudaStreamSynchronize(st));
+    ep.n_vrows = n_vrows;
+    if ((rc = dev_alloc(&ep.vsrc, (size_t) E, &a->device_bytes)) || (rc = dev_alloc(&ep.vstart, (size_t) n_vrows + 1, &a->device_bytes)) ||
+        (rc = dev_alloc(&ep.vnbr, (size_t) 27 * std::max(n_active, 1), &a->device_bytes))) { cleanup(); return rc; }
+    EP_CHECK(cudaMemsetAsync(ep.vnbr, 0xFF, (size_t) 27 * std::max(n_active, 1) * sizeof(int32_t), st));       // APRNET_NONE
+    EP_CHECK(cudaMemsetAsync(ep.vstart, 0, ((size_t) n_vrows + 1) * sizeof(int32_t), st));
+    if (n_active) vrow_fill_kernel<<<aprnet_ceil_div(n_active, 128), 128, 0, st>>>(ep.active, n_active, tgt_ptr, tgt_edge, src, tb, vfirst, E,
+                                                                                  ep.vstart, ep.vnbr, ep.vsrc);
+
+    // ranges of active[] by level of the locations their edges come from, and the chunk map
+    const int cml = a->cml(dl);
+    std::vector<ll> key_h;
+    std::vector<int> key_level;
+    for (int l = a->meta.level_min; l <= cml; ++l) {        // particle targets of level l <- locations of level l + 1
+        key_h.push_back(a->meta.lvl_begin[l]); key_level.push_back(l + 1);
+    }
+    for (int l = a->meta.level_min - 1; l <= cml - 1; ++l) {    // tree targets of level l <- locations of level l
+        key_h.push_back(N + a->meta.tlvl_begin[l]); key_level.push_back(l);
+    }
+    key_h.push_back(NT); key_level.push_back(-1);
+    const int nkeys = (int) key_h.size();
+    const int nchunk = (int) (n_vrows / VROW_GRANULE) + 1;
+    EP_CHECK(cudaMalloc((void**) &keys, (size_t) std::max(nkeys, nchunk + 1) * sizeof(ll)));
+    EP_CHECK(cudaMalloc((void**) &found, (size_t) std::max(nkeys, nchunk + 1) * sizeof(ll)));
+    std::vector<ll> found_h(std::max(nkeys, nchunk + 1));
+    EP_CHECK(cudaMemcpyAsync(keys, key_h.data(), nkeys * sizeof(ll), cudaMemcpyHostToDevice, st));
+    lower_bound_kernel<<<1, 64, 0, st>>>(ep.active, n_active, keys, nkeys, found);
+    EP_CHECK(cudaMemcpyAsync(found_h.data(), found, nkeys * sizeof(ll), cudaMemcpyDeviceToHost, st));
+    EP_CHECK(cudaStreamSynchronize(st));
+    ep.segs.clear();
+    for (int k = 0; k + 1 < nkeys; ++k) {
+        ActiveSeg sg; sg.begin = found_h[k]; sg.end = found_h[k + 1]; sg.location_level = key_level[k];
+        if (sg.end > sg.begin && sg.location_level >= a->meta.level_min && sg.location_level <= cml) ep.segs.push_back(sg);
+        else if (sg.end > sg.begin) { aprnet_set_error("edge plan: edges from level %d outside [%d, %d]", sg.location_level, a->meta.level_min, cml); cleanup(); return APRNET_ERR_CUDA; }
+    }
+    std::vector<ll> ckey(nchunk + 1);
+    for (int k = 0; k < nchunk; ++k) ckey[k] = (ll) k * VROW_GRANULE;
+    ckey[nchunk] = (ll) n_vrows + 1;        // beyond the last value: maps to n_active
+    EP_CHECK(cudaMemcpyAsync(keys, ckey.data(), (nchunk + 1) * sizeof(ll), cudaMemcpyHostToDevice, st));
+    lower_bound_kernel<<<aprnet_ceil_div(nchunk + 1, 64), 64, 0, st>>>(vfirst, n_active, keys, nchunk + 1, found);
+    EP_CHECK(cudaMemcpyAsync(found_h.data(), found, (nchunk + 1) * sizeof(ll), cudaMemcpyDeviceToHost, st));
+    EP_CHECK(cudaStreamSynchronize(st));
+    std::vector<int32_t> vf(nchunk + 1);
+    ep.chunk_a.clear(); ep.chunk_v.clear();
+    for (int k = 0; k <= nchunk; ++k) {
+        const ll ca = std::min<ll>(found_h[k], n_active);
+        if (!ep.chunk_a.empty() && ep.chunk_a.back() == ca) continue;
+        int32_t v = 0;
+        EP_CHECK(cudaMemcpyAsync(&v, vfirst + ca, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+        EP_CHECK(cudaStreamSynchronize(st));
+        ep.chunk_a.push_back(ca); ep.chunk_v.push_back(v);
+    }
+    if (ep.chunk_a.back() != n_active) { ep.chunk_a.push_back(n_active); ep.chunk_v.push_back(n_vrows); }
     EP_CHECK(cudaGetLastError());
     EP_CHECK(cudaStreamSynchronize(st));
 #undef EP_CHECK
@@ -215,50 +303,56 @@ extern "C" int aprnet_edge_plan_build(aprnet_apr* a, int dl, void* stream) {
     return aprnet_get_edge_plan(a, dl, (cudaStream_t) stream) ? APRNET_OK : APRNET_ERR_CUDA;
 }
 
-extern "C" int64_t aprnet_edge_workspace_bytes(const aprnet_apr* a, int dl, int cin) {
+extern "C" int64_t aprnet_edge_workspace_bytes(const aprnet_apr* a, int dl, int cout) {
     if (!a || !a->valid_dl(dl)) return -1;
-    const ll cap = 8ll << 30;     // bounds the edge-row workspace; larger = fewer pull passes over the target list
-    const ll all = 27 * a->number_parts(dl) * (ll) aprnet_tc_pad(cin) * 4;
-    return (int64_t) std::max<ll>(256, std::min(cap, all));
+    const ll cap = 8ll << 30;     // bounds the virtual-row workspace; smaller = more passes
+    const ll row = (ll) aprnet_tc_pad(cout) * 2;
+    auto it = a->edge_plans.find(dl);
+    const ll rows = it != a->edge_plans.end() ? it->second.n_vrows + 2 : 27 * a->number_parts(dl) + 2;
+    return (int64_t) std::max<ll>(256, std::min(cap, rows * row));
 }
 
-// Cross-level part of the input gradient (added to grad_input / grad_tree, which the call zero-fills)
-// followed by the tree adjoint.  packed_grad_output_rows: channels-last bf16 dO rows with a zero row at
-// index N; weights fp32 (slots, Cout, Cin, 27); wp_ws: space for the packed transposed weights;
-// edge_ws: aprnet_edge_workspace_bytes() bytes.
+// Cross-level part of the input gradient (added to grad_input, which holds the same-level part, and to
+// grad_tree, which the call zero-fills) followed by the tree adjoint.  packed_grad_output_rows:
+// channels-last bf16 dO rows; weights fp32 (slots, Cout, Cin, 27); wp_ws: space for the packed
+// transposed weights; edge_ws: aprnet_edge_workspace_bytes() bytes.
 extern "C" int aprnet_conv333_backward_input_cross_level_tc(aprnet_apr* a, int dl, int cin, int cout, int slots,
                                                             const void* grows, int gpad, const float* w, float* gin,
                                                             int64_t ld_in, float* gtree, int64_t ld_tree, void* wp_ws,
                                                             void* edge_ws, int64_t edge_ws_bytes, void* stream) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && cin > 0 && cout > 0 && slots > 0 && grows && w && gin && gtree && wp_ws && edge_ws, "bad argument");
+    APRNET_ARG_CHECK(gpad == aprnet_tc_pad(cout), "packed row width does not match the padded channel count");
     cudaStream_t st = (cudaStream_t) stream;
     EdgePlan* ep = aprnet_get_edge_plan(a, dl, st);
     if (!ep) return APRNET_ERR_CUDA;
-    const ll N = a->number_parts(dl), ts = a->tree_size(dl);
+    const ll ts = a->tree_size(dl);
     if (ts > 0) APRNET_CUDA_CHECK(cudaMemset2DAsync(gtree, (size_t) ld_tree * sizeof(float), 0, (size_t) ts * sizeof(float), (size_t) cin, st));
-    const int row_pad = aprnet_tc_pad(cin);
-    const ll cap_edges = edge_ws_bytes / ((ll) row_pad * 4);
-    int rc = aprnet_tc_pack_weights(w, slots, cin, cout, 2, wp_ws, st);
-    if (rc) return rc;
-    const int ng = (int) ep->groups.size();
-    int g0 = 0;
-    while (g0 < ng) {
-        int g1 = g0;
-        ll cnt = 0;
-        while (g1 < ng && cnt + (ep->groups[g1].end - ep->groups[g1].begin) <= cap_edges) { cnt += ep->groups[g1].end - ep->groups[g1].begin; ++g1; }
-        if (g1 == g0) { aprnet_set_error("edge workspace too small for one (tap, level) group of %lld edges", (ll) (ep->groups[g0].end - ep->groups[g0].begin)); return APRNET_ERR_ARG; }
-        rc = aprnet_tc_edge_gemm(a, dl, cin, cout, slots, grows, gpad, N, wp_ws, ep, g0, g1, (float*) edge_ws, row_pad, st);
+    if (ep->n_active > 0) {
+        int rc = aprnet_tc_pack_weights(w, slots, cin, cout, 2, wp_ws, st);
         if (rc) return rc;
-        const ll e0 = ep->groups[g0].begin, e1 = ep->groups[g1 - 1].end;
-        if (ep->n_active > 0) {
-            dim3 grid((unsigned) aprnet_ceil_div(ep->n_active, 128), (unsigned) (row_pad / 16));
-            { AprnetProfScope _prof("edge_pull", st);
-            edge_pull_kernel<<<grid, 128, 0, st>>>(ep->active, ep->n_active, ep->tgt_ptr, ep->tgt_edge, e0, e1, (const float*) edge_ws, row_pad,
-                                                   gin, ld_in, gtree, ld_tree, N, cin);
+        __nv_bfloat16* vrows = reinterpret_cast<__nv_bfloat16*>(edge_ws);
+        APRNET_CUDA_CHECK(cudaMemsetAsync(vrows, 0, (size_t) gpad * 2, st));          // row 0: zeros
+        const ll cap_rows = edge_ws_bytes / ((ll) gpad * 2) - 1;
+        const int nk = (int) ep->chunk_a.size() - 1;
+        int k0 = 0;
+        while (k0 < nk) {
+            int k1 = k0 + 1;
+            while (k1 < nk && ep->chunk_v[k1 + 1] - ep->chunk_v[k0] <= cap_rows) ++k1;
+            const ll v0 = ep->chunk_v[k0], v1 = ep->chunk_v[k1], a0 = ep->chunk_a[k0], a1 = ep->chunk_a[k1];
+            if (v1 - v0 > cap_rows) { aprnet_set_error("edge workspace too small for %lld virtual rows", v1 - v0); return APRNET_ERR_ARG; }
+            if (v1 > v0) {
+                { AprnetProfScope _prof("edge_reduce", st);
+                vrow_reduce_kernel<<<aprnet_ceil_div((v1 - v0) * (gpad / 8), 256), 256, 0, st>>>(ep->vstart, ep->vsrc, v0, v1,
+                                                                                            (const __nv_bfloat16*) grows, gpad, vrows);
+                }
+                APRNET_LAUNCH_CHECK();
+                // row index r of the gather = virtual row id; the zero row is addressed as v0 - 1
+                rc = aprnet_tc_gather_targets(a, dl, cin, cout, slots, vrows + (1 - v0) * gpad, gpad, v0 - 1, wp_ws, ep, a0, a1,
+                                              gin, ld_in, gtree, ld_tree, st);
+                if (rc) return rc;
             }
-            APRNET_LAUNCH_CHECK();
+            k0 = k1;
         }
-        g0 = g1;
     }
     return aprnet_fill_tree_mean_backward(a, dl, APRNET_F32, cin, gin, ld_in, gtree, ld_tree, st);
 }

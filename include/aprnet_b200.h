@@ -165,7 +165,7 @@ int aprnet_conv333_backward_input_cross_level(aprnet_apr* apr, int level_delta, 
  * per-target pull (deterministic).  The edge lists of a level delta are built once and cached
  * (aprnet_edge_plan_build allocates; call it up front).  edge_ws: aprnet_edge_workspace_bytes() bytes. */
 int aprnet_edge_plan_build(aprnet_apr* apr, int level_delta, void* stream);
-int64_t aprnet_edge_workspace_bytes(const aprnet_apr* apr, int level_delta, int cin);
+int64_t aprnet_edge_workspace_bytes(const aprnet_apr* apr, int level_delta, int cout);
 int aprnet_conv333_backward_input_cross_level_tc(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
                                                  const void* packed_grad_output_rows, int grad_output_row_width,
                                                  const float* weights, float* grad_input, int64_t ld_in,

@@ -59,7 +59,9 @@ def test_conv333_tensor_core_path(name, cin, cout, nst, oracle, bf16_mode):
             gi, gw = C.conv333_backward(APRPtrVector([apr]), xt, wt, got, ld)
             want = o.conv333_forward(x.astype(np.float64), w.astype(np.float64), dl)
             gi_ref, gw_ref = o.conv333_backward(x.astype(np.float64), w.astype(np.float64), go.astype(np.float64), dl)
-            tol_out, tol_gi = (5e-3, 1e-4) if exact_inputs else (2e-2, 2e-2)
+            # inputs that are exact in bf16 leave only the fp32 accumulation order (outputs: 27 * cin terms) and, for the input
+            # gradient, the bf16 rounding of the per-(target, tap) sums of grad_output rows of the cross-level part
+            tol_out, tol_gi = (5e-3, 5e-3) if exact_inputs else (2e-2, 2e-2)
             assert H.rel_err(H.t2n(out[0]), want) <= tol_out, (name, dl, exact_inputs)
             assert H.rel_err(H.t2n(gi[0]), gi_ref) <= tol_gi, (name, dl, exact_inputs)
             assert H.rel_err(H.t2n(gw), gw_ref) <= tol_out, (name, dl, exact_inputs)
