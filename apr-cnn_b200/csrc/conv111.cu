@@ -53,7 +53,19 @@ __global__ void __launch_bounds__(TPB) conv111_kernel(SegTable segs, const T* __
     T acc[OB];
 #pragma unroll
     for (int o = 0; o < OB; ++o) acc[o] = 0;
-    for (int i = 0; i < n_in; ++i) {
+    int i = 0;
+    for (; i + 8 <= n_in; i += 8) {          // eight independent loads in flight per thread
+        T v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = in[(ll) (i + k) * ld_in + p];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const T* wr = wsm + (i + k) * OB;
+#pragma unroll
+            for (int o = 0; o < OB; ++o) acc[o] = fma(v[k], wr[o], acc[o]);
+        }
+    }
+    for (; i < n_in; ++i) {
         const T v = in[(ll) i * ld_in + p];
         const T* wr = wsm + i * OB;
 #pragma unroll
@@ -107,6 +119,55 @@ __global__ void __launch_bounds__(256) conv111_dw_partial_kernel(ll seg_begin, l
         }
 }
 
+// Weight gradient for few output channels (CO <= 4, e.g. a classification head): a lane owns one particle
+// of a 32-particle strip and keeps the CO x 32 products of one block of 32 input channels; strips are
+// visited in a fixed order, lanes and warps are combined in a fixed order.
+template<typename T, int CO>
+__global__ void __launch_bounds__(256) conv111_dw_small_kernel(ll seg_begin, ll seg_end, ll chunk_len,
+                                                               const T* __restrict__ in, ll ld_in,
+                                                               const T* __restrict__ gout, ll ld_out,
+                                                               T* __restrict__ partial, int cin, int cout) {
+    __shared__ T red[8][CO * 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int i0 = blockIdx.y * 32;
+    const ll pb = seg_begin + (ll) blockIdx.x * chunk_len;
+    const ll pe = min(seg_end, pb + chunk_len);
+    T acc[CO][32];
+#pragma unroll
+    for (int o = 0; o < CO; ++o)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[o][i] = 0;
+    for (ll p = pb + warp * 32 + lane; p < pe; p += 256) {
+        T g[CO];
+#pragma unroll
+        for (int o = 0; o < CO; ++o) g[o] = o < cout ? gout[(ll) o * ld_out + p] : T(0);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const T x = i0 + i < cin ? in[(ll) (i0 + i) * ld_in + p] : T(0);
+#pragma unroll
+            for (int o = 0; o < CO; ++o) acc[o][i] = fma(g[o], x, acc[o][i]);
+        }
+    }
+#pragma unroll
+    for (int o = 0; o < CO; ++o)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            T v = acc[o][i];
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+            if (lane == 0) red[warp][o * 32 + i] = v;
+        }
+    __syncthreads();
+    T* dst = partial + (ll) blockIdx.x * cout * cin;
+    for (int e = threadIdx.x; e < CO * 32; e += 256) {
+        const int o = e / 32, i = i0 + e % 32;
+        T v = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v += red[w][e];
+        if (o < cout && i < cin) dst[(ll) o * cin + i] = v;
+    }
+}
+
 // dst[e] += sum_{c < nchunks} partial[c][e], chunks visited in ascending order
 template<typename T>
 __global__ void reduce_partial_kernel(const T* __restrict__ partial, int nchunks, ll elems, T* __restrict__ dst) {
@@ -117,15 +178,12 @@ __global__ void reduce_partial_kernel(const T* __restrict__ partial, int nchunks
     dst[e] += s;
 }
 
-constexpr int DW_MAX_CHUNKS = 128;
+// block partials of the weight gradient: many chunks for small filters (parallelism), fewer for large ones (workspace)
+inline int dw_max_chunks(int cin, int cout) { return (int) std::max<ll>(128, std::min<ll>(2048, (16ll << 20) / ((ll) cin * cout))); }
 
-template<typename T>
-int conv111_apply(const aprnet_apr* a, int dl, int n_in, int n_out, int S, const T* in, ll ld_in, const T* w,
-                  ll ws, ll wo, ll wi, T* out, ll ld_out, cudaStream_t st) {
-    constexpr int OB = 16, TPB = 256;
-    const SegTable segs = make_seg_table(aprnet_segments(a, dl, S, true), TPB);
-    const int tiles = segs.tile_begin[segs.n];
-    if (tiles == 0) return APRNET_OK;
+template<typename T, int OB, int TPB>
+int conv111_launch(const SegTable& segs, int tiles, const T* in, ll ld_in, const T* w, ll ws, ll wo, ll wi, T* out, ll ld_out,
+                   int n_in, int n_out, cudaStream_t st) {
     const size_t smem = (size_t) n_in * OB * sizeof(T);
     if (smem > 48 * 1024)
         APRNET_CUDA_CHECK(cudaFuncSetAttribute(conv111_kernel<T, OB, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
@@ -138,17 +196,30 @@ int conv111_apply(const aprnet_apr* a, int dl, int n_in, int n_out, int S, const
 }
 
 template<typename T>
+int conv111_apply(const aprnet_apr* a, int dl, int n_in, int n_out, int S, const T* in, ll ld_in, const T* w,
+                  ll ws, ll wo, ll wi, T* out, ll ld_out, cudaStream_t st) {
+    constexpr int TPB = 256;
+    const SegTable segs = make_seg_table(aprnet_segments(a, dl, S, true), TPB);
+    const int tiles = segs.tile_begin[segs.n];
+    if (tiles == 0) return APRNET_OK;
+    if (n_out <= 4) return conv111_launch<T, 4, TPB>(segs, tiles, in, ld_in, w, ws, wo, wi, out, ld_out, n_in, n_out, st);      // e.g. a classification head
+    if (n_out <= 16) return conv111_launch<T, 16, TPB>(segs, tiles, in, ld_in, w, ws, wo, wi, out, ld_out, n_in, n_out, st);
+    return conv111_launch<T, 32, TPB>(segs, tiles, in, ld_in, w, ws, wo, wi, out, ld_out, n_in, n_out, st);      // the input is read once per 32 outputs
+}
+
+template<typename T>
 int conv111_dw(const aprnet_apr* a, int dl, int cin, int cout, int S, const T* in, ll ld_in, const T* gout, ll ld_out,
                T* gw, T* partial, cudaStream_t st) {
     const std::vector<Segment> segs = aprnet_segments(a, dl, S, true);
     const ll elems = (ll) cin * cout;
     for (const Segment& s : segs) {
         const ll len = s.end - s.begin;
-        const int nchunks = (int) std::min<ll>(DW_MAX_CHUNKS, (len + 1023) / 1024);
+        const int nchunks = (int) std::min<ll>(dw_max_chunks(cin, cout), (len + 1023) / 1024);
         const ll chunk_len = ((len + nchunks - 1) / nchunks + 31) / 32 * 32;
         dim3 grid((unsigned) nchunks, (unsigned) (aprnet_ceil_div(cout, 32) * aprnet_ceil_div(cin, 32)));
         { AprnetProfScope _prof("conv111_dw", st);
-        conv111_dw_partial_kernel<T><<<grid, 256, 0, st>>>(s.begin, s.end, chunk_len, in, ld_in, gout, ld_out, partial, cin, cout);
+        if (cout <= 4) conv111_dw_small_kernel<T, 4><<<grid, 256, 0, st>>>(s.begin, s.end, chunk_len, in, ld_in, gout, ld_out, partial, cin, cout);
+        else conv111_dw_partial_kernel<T><<<grid, 256, 0, st>>>(s.begin, s.end, chunk_len, in, ld_in, gout, ld_out, partial, cin, cout);
         }
         { AprnetProfScope _prof("conv111_dw_reduce", st);
         reduce_partial_kernel<T><<<aprnet_ceil_div(elems, 256), 256, 0, st>>>(partial, nchunks, elems, gw + (ll) s.slot * elems);
@@ -272,7 +343,7 @@ extern "C" int aprnet_conv111_backward_input(const aprnet_apr* a, int dl, int dt
              conv111_apply<double>(a, dl, cout, cin, S, (const double*) gout, ld_out, (const double*) w, ws, 1, cin, (double*) gin, ld_in, st));
 }
 
-extern "C" int64_t aprnet_conv111_partial_elems(int cin, int cout) { return (int64_t) DW_MAX_CHUNKS * cin * cout; }
+extern "C" int64_t aprnet_conv111_partial_elems(int cin, int cout) { return (int64_t) dw_max_chunks(cin, cout) * cin * cout; }
 
 extern "C" int aprnet_conv111_backward_weights(const aprnet_apr* a, int dl, int dtype, int cin, int cout, int S,
                                                const void* in, int64_t ld_in, const void* gout, int64_t ld_out,
