@@ -21,6 +21,7 @@
 #include <memory>
 #include <sstream>
 #include <string>
+#include <array>
 #include <vector>
 
 #include "../../include/aprnet_b200.h"
@@ -451,6 +452,91 @@ torch::Tensor upsample_const_backward(std::vector<APR*>& aprs, torch::Tensor gra
     return grad_input;
 }
 
+// ---- particles <-> dense image (wrap_reconstruct_gpu.hpp:29-98, wrap_sample_particles_gpu.hpp:29-98) ----
+static std::array<int64_t, 3> image_extent(std::vector<APR*>& aprs, const std::vector<int>& dl, const torch::Tensor& like) {
+    std::array<int64_t, 3> e = {0, 0, 0};
+    for (size_t i = 0; i < aprs.size(); ++i) {
+        int z, x, y;
+        check(aprnet_image_dims(aprs[i]->handle(like), dl[i], &z, &x, &y), "image_dims");
+        e[0] = std::max<int64_t>(e[0], z); e[1] = std::max<int64_t>(e[1], x); e[2] = std::max<int64_t>(e[2], y);
+    }
+    return e;
+}
+
+// the C functions take one image of exactly the APR's extents; a batch whose APRs differ in size is padded
+static void check_same_extent(std::vector<APR*>& aprs, const std::vector<int>& dl, const torch::Tensor& like, const std::array<int64_t, 3>& e) {
+    for (size_t i = 0; i < aprs.size(); ++i) {
+        int z, x, y;
+        check(aprnet_image_dims(aprs[i]->handle(like), dl[i], &z, &x, &y), "image_dims");
+        TORCH_CHECK(z == e[0] && x == e[1] && y == e[2], "all APRs of a batch must have the same image extents at their level_delta");
+    }
+}
+
+torch::Tensor reconstruct_forward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor level_delta) {
+    CHECK_INPUT(input);
+    check_batch(aprs, input);
+    c10::cuda::CUDAGuard guard(input.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    for (size_t i = 0; i < aprs.size(); ++i) check_level_delta(*aprs[i], dl[i]);
+    const auto e = image_extent(aprs, dl, input);
+    check_same_extent(aprs, dl, input, e);
+    auto output = torch::empty({input.size(0), input.size(1), e[0], e[1], e[2]}, input.options());
+    for (int64_t b = 0; b < input.size(0); ++b)
+        check(aprnet_reconstruct_forward(aprs[b]->handle(input), dl[b], dtype_id(input), (int) input.size(1), row(input, b), input.size(2),
+                                         row(output, b), stream_of(input)), "reconstruct_forward");
+    return output;
+}
+
+torch::Tensor reconstruct_backward(std::vector<APR*>& aprs, torch::Tensor grad_output, torch::Tensor level_delta) {
+    CHECK_INPUT(grad_output);
+    TORCH_CHECK(grad_output.dim() == 5 && (size_t) grad_output.size(0) == aprs.size(), "expected (batch, channels, z, x, y)");
+    c10::cuda::CUDAGuard guard(grad_output.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    int64_t max_size = 0;
+    for (size_t i = 0; i < aprs.size(); ++i) { check_level_delta(*aprs[i], dl[i]); max_size = std::max(max_size, aprs[i]->number_parts(dl[i])); }
+    check_same_extent(aprs, dl, grad_output, {grad_output.size(2), grad_output.size(3), grad_output.size(4)});
+    auto grad_input = torch::empty({grad_output.size(0), grad_output.size(1), max_size}, grad_output.options());
+    for (int64_t b = 0; b < grad_output.size(0); ++b) {
+        check(aprnet_reconstruct_backward(aprs[b]->handle(grad_output), dl[b], dtype_id(grad_output), (int) grad_output.size(1), row(grad_output, b),
+                                          row(grad_input, b), max_size, stream_of(grad_output)), "reconstruct_backward");
+        zero_padding(grad_input, b, aprs[b]->number_parts(dl[b]));
+    }
+    return grad_input;
+}
+
+torch::Tensor sample_particles_forward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor level_delta) {
+    CHECK_INPUT(input);
+    TORCH_CHECK(input.dim() == 5 && (size_t) input.size(0) == aprs.size(), "expected (batch, channels, z, x, y)");
+    c10::cuda::CUDAGuard guard(input.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    int64_t max_size = 0;
+    for (size_t i = 0; i < aprs.size(); ++i) { check_level_delta(*aprs[i], dl[i]); max_size = std::max(max_size, aprs[i]->number_parts(dl[i])); }
+    check_same_extent(aprs, dl, input, {input.size(2), input.size(3), input.size(4)});
+    auto output = torch::empty({input.size(0), input.size(1), max_size}, input.options());
+    for (int64_t b = 0; b < input.size(0); ++b) {
+        check(aprnet_sample_particles_forward(aprs[b]->handle(input), dl[b], dtype_id(input), (int) input.size(1), row(input, b),
+                                              row(output, b), max_size, stream_of(input)), "sample_particles_forward");
+        zero_padding(output, b, aprs[b]->number_parts(dl[b]));
+    }
+    return output;
+}
+
+torch::Tensor sample_particles_backward(std::vector<APR*>& aprs, torch::Tensor grad_output, torch::Tensor level_delta) {
+    CHECK_INPUT(grad_output);
+    check_batch(aprs, grad_output);
+    c10::cuda::CUDAGuard guard(grad_output.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    for (size_t i = 0; i < aprs.size(); ++i) check_level_delta(*aprs[i], dl[i]);
+    const auto e = image_extent(aprs, dl, grad_output);
+    check_same_extent(aprs, dl, grad_output, e);
+    auto grad_input = torch::empty({grad_output.size(0), grad_output.size(1), e[0], e[1], e[2]}, grad_output.options());
+    for (int64_t b = 0; b < grad_output.size(0); ++b)
+        check(aprnet_sample_particles_backward(aprs[b]->handle(grad_output), dl[b], dtype_id(grad_output), (int) grad_output.size(1),
+                                               row(grad_output, b), grad_output.size(2), row(grad_input, b), stream_of(grad_output)),
+              "sample_particles_backward");
+    return grad_input;
+}
+
 // ---- fused GroupNorm + ReLU ---------------------------------------------------------------------------
 std::vector<torch::Tensor> groupnorm_relu_forward(torch::Tensor x, c10::optional<torch::Tensor> gamma, c10::optional<torch::Tensor> beta,
                                                   int64_t groups, double eps, bool relu) {
@@ -607,6 +693,10 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
     cuda.def("conv333_backward_with_tree", &conv333_backward_with_tree, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a, "tree"_a, "need_grad_input"_a = true);
     cuda.def("upsample_const_forward", &upsample_const_forward, "aprs"_a, "input"_a, "level_delta"_a);
     cuda.def("upsample_const_backward", &upsample_const_backward, "aprs"_a, "grad_output"_a, "level_delta"_a);
+    cuda.def("reconstruct_forward", &reconstruct_forward, "aprs"_a, "input"_a, "level_delta"_a);
+    cuda.def("reconstruct_backward", &reconstruct_backward, "aprs"_a, "grad_output"_a, "level_delta"_a);
+    cuda.def("sample_particles_forward", &sample_particles_forward, "aprs"_a, "input"_a, "level_delta"_a);
+    cuda.def("sample_particles_backward", &sample_particles_backward, "aprs"_a, "grad_output"_a, "level_delta"_a);
     cuda.def("restrict_kernel333_forward", &restrict_kernel_333_forward, "weights"_a, "num_levels"_a);
     cuda.def("restrict_kernel333_backward", &restrict_kernel_333_backward, "grad_weights_expanded"_a, "num_levels"_a);
     cuda.def("groupnorm_relu_forward", &groupnorm_relu_forward, "x"_a, "gamma"_a, "beta"_a, "groups"_a, "eps"_a, "relu"_a);

@@ -239,6 +239,24 @@ int aprnet_upsample_backward(const aprnet_apr* apr, int level_delta, int dtype, 
                              const void* grad_output, int64_t ld_out, void* grad_input, int64_t ld_in,
                              void* stream);
 
+/* ---- particles <-> dense image at level_max - level_delta -------------------------------------
+ * Replace apply_reconstruct / apply_reconstruct_backward (pyapr/aprnet/cuda/src/reconstruct_gpu.cu:159-225)
+ * and apply_sample_particles / _backward (sample_particles_gpu.cu:172-246).  image: (channels, Z, X, Y)
+ * contiguous with the extents of aprnet_image_dims(); particle tensors: (channels, ld).
+ * reconstruct: piecewise-constant image from particle values; its backward sums the image gradient over
+ * each particle's cell.  sample_particles: mean of the image over each particle's cell (cells are clipped
+ * at the volume border); its backward spreads value / cell volume over the cell.  Every output element
+ * has exactly one writer (no atomics). */
+int aprnet_image_dims(const aprnet_apr* apr, int level_delta, int* z_num, int* x_num, int* y_num);
+int aprnet_reconstruct_forward(const aprnet_apr* apr, int level_delta, int dtype, int channels,
+                               const void* input, int64_t ld_in, void* image, void* stream);
+int aprnet_reconstruct_backward(const aprnet_apr* apr, int level_delta, int dtype, int channels,
+                                const void* grad_image, void* grad_input, int64_t ld_in, void* stream);
+int aprnet_sample_particles_forward(const aprnet_apr* apr, int level_delta, int dtype, int channels,
+                                    const void* image, void* output, int64_t ld_out, void* stream);
+int aprnet_sample_particles_backward(const aprnet_apr* apr, int level_delta, int dtype, int channels,
+                                     const void* grad_output, int64_t ld_out, void* grad_image, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -171,3 +171,85 @@ def restrict333_backward(gw, num_stencils):
     fn = getattr(lib(), "orc_restrict333_backward_" + _SFX[gw.dtype])
     fn(int(num_stencils), gw.shape[0], C.c_int64(gw.shape[1] * gw.shape[2]), _p(gw), _p(out))
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# particles <-> dense image (numpy restatement; the reference has only CUDA code for these:
+# pyapr/aprnet/cuda/src/reconstruct_gpu.cu:5-157, sample_particles_gpu.cu:5-170).  Pinned relationally
+# like the reference's own tests (gradcheck and sample(reconstruct(x)) == x, pyapr/tests/test_aprnet.py:248-285).
+# ---------------------------------------------------------------------------------------------
+def _cells(a, dl):
+    """Yield (feature index array, z0, x0, y0, edge) per particle / upgraded node for level_delta dl."""
+    cml = a.level_max - dl
+    row_off, tree_row_off = {}, {}
+    r = 0
+    for l in range(a.level_min, a.level_max + 1):
+        row_off[l] = r
+        r += a.dims[l][0] * a.dims[l][1]
+    r = 0
+    for l in range(0, a.level_max):
+        tree_row_off[l] = r
+        r += a.dims[l][0] * a.dims[l][1]
+    out = []
+
+    def level_cells(row_ptr, y, off, l, edge, index_offset):
+        zn, xn, _ = a.dims[l]
+        rp = row_ptr[off:off + zn * xn + 1]
+        counts = np.diff(rp)
+        rows = np.repeat(np.arange(zn * xn), counts)
+        idx = np.arange(rp[0], rp[-1])
+        return idx + index_offset, (rows // xn) * edge, (rows % xn) * edge, y[rp[0]:rp[-1]].astype(np.int64) * edge, edge
+
+    for l in range(a.level_min, cml + 1):
+        out.append(level_cells(a.row_ptr, a.y, row_off[l], l, 1 << (cml - l), 0))
+    if dl > 0:
+        n_le = int(a.row_ptr[row_off[cml] + a.dims[cml][0] * a.dims[cml][1]])                # particles of levels <= cml
+        t_begin = int(a.tree_row_ptr[tree_row_off[cml]])
+        out.append(level_cells(a.tree_row_ptr, a.tree_y, tree_row_off[cml], cml, 1, n_le - t_begin))
+    return out, a.dims[cml]
+
+
+def reconstruct_forward(a, x, dl):
+    """x (C, N) -> image (C, Z, X, Y)."""
+    cells, (Z, X, Y) = _cells(a, dl)
+    img = np.zeros((x.shape[0], Z, X, Y), dtype=x.dtype)
+    for idx, z0, x0, y0, e in cells:
+        for dz in range(e):
+            for dx in range(e):
+                for dy in range(e):
+                    ok = (z0 + dz < Z) & (x0 + dx < X) & (y0 + dy < Y)
+                    img[:, z0[ok] + dz, x0[ok] + dx, y0[ok] + dy] = x[:, idx[ok]]
+    return img
+
+
+def reconstruct_backward(a, gimg, dl, n):
+    """image gradient (C, Z, X, Y) -> (C, n)."""
+    cells, (Z, X, Y) = _cells(a, dl)
+    g = np.zeros((gimg.shape[0], n), dtype=gimg.dtype)
+    for idx, z0, x0, y0, e in cells:
+        for dz in range(e):
+            for dx in range(e):
+                for dy in range(e):
+                    ok = (z0 + dz < Z) & (x0 + dx < X) & (y0 + dy < Y)
+                    g[:, idx[ok]] += gimg[:, z0[ok] + dz, x0[ok] + dx, y0[ok] + dy]
+    return g
+
+
+def _cell_volume(z0, x0, y0, e, Z, X, Y):
+    return (np.minimum(z0 + e, Z) - z0) * (np.minimum(x0 + e, X) - x0) * (np.minimum(y0 + e, Y) - y0)
+
+
+def sample_particles_forward(a, img, dl, n):
+    out = reconstruct_backward(a, img, dl, n)
+    cells, (Z, X, Y) = _cells(a, dl)
+    for idx, z0, x0, y0, e in cells:
+        out[:, idx] /= _cell_volume(z0, x0, y0, e, Z, X, Y)
+    return out
+
+
+def sample_particles_backward(a, g, dl):
+    cells, (Z, X, Y) = _cells(a, dl)
+    scaled = g.copy()
+    for idx, z0, x0, y0, e in cells:
+        scaled[:, idx] /= _cell_volume(z0, x0, y0, e, Z, X, Y)
+    return reconstruct_forward(a, scaled, dl)

@@ -159,3 +159,23 @@ def test_generated_structures_are_valid(name, oracle):
         assert nb.shape == (27, o.number_parts(dl))
         assert (nb[13] == np.arange(nb.shape[1])).all()          # the centre tap is the location itself
         assert ct.shape[0] == 8
+
+
+def test_image_ops_restatement_round_trip_and_adjoint():
+    """numpy restatement of Reconstruct / SampleParticles: the reconstruction covers every voxel once,
+    sample(reconstruct(x)) == x (pyapr/tests/test_aprnet.py:272-285) and backward is the adjoint of forward."""
+    import apr_oracle
+    a = H.arrays("odd")
+    o = apr_oracle.OracleAPR(a)
+    rng = np.random.RandomState(0)
+    for dl in range(0, H.max_dl(a) + 1):
+        n = o.number_parts(dl)
+        x = rng.rand(2, n)
+        img = apr_oracle.reconstruct_forward(a, x, dl)
+        ones = apr_oracle.reconstruct_forward(a, np.ones((1, n)), dl)
+        assert (ones == 1).all()
+        assert np.abs(apr_oracle.sample_particles_forward(a, img, dl, n) - x).max() < 1e-14
+        g = rng.randn(*img.shape)
+        assert abs((img * g).sum() - (x * apr_oracle.reconstruct_backward(a, g, dl, n)).sum()) < 1e-9
+        s = apr_oracle.sample_particles_forward(a, g, dl, n)
+        assert abs((s * x).sum() - (g * apr_oracle.sample_particles_backward(a, x, dl)).sum()) < 1e-9
