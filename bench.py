@@ -456,6 +456,15 @@ def run_layer(args):
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1; the contract is ONE JSON line on
+    # stdout, so everything else goes to stderr and the result is written to the saved descriptor at the end.
+    sys.stdout.flush()
+    result_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj):
+        os.write(result_fd, (json.dumps(obj) + "\n").encode())
+
     if args.impl == "reference":
         if rank != 0:
             return
@@ -466,11 +475,11 @@ def main():
                "config": {"workload": "4-level APR U-Net fwd+bwd+SGD, reference CPU operators on host cores, bounded sample: " + cb["sample"]},
                "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
                "e2e": {"value": cb["value"], "unit": "particles/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(out))
+        emit(out)
         return
     out = run_layer(args) if args.layer else run_gpu(args)
     if out is not None:
-        print(json.dumps(out))
+        emit(out)
 
 
 if __name__ == "__main__":
