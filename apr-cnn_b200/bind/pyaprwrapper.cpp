@@ -232,6 +232,73 @@ std::vector<torch::Tensor> conv333_forward_keep_tree(std::vector<APR*>& aprs, to
     return conv333_forward_impl(aprs, input, weights, level_delta, true);
 }
 
+// Tensor-core forward that keeps the packed bf16 rows of the input (particles, tree means, zero row) for the
+// backward pass instead of the fp32 input and the tree means: returns {output, rows (B, bytes) uint8}.
+std::vector<torch::Tensor> conv333_forward_keep_rows(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights, torch::Tensor level_delta) {
+    CHECK_INPUT(input); CHECK_INPUT(weights);
+    check_batch(aprs, input);
+    TORCH_CHECK(weights.dim() == 6 && weights.size(3) == 3 && weights.size(4) == 3 && weights.size(5) == 3, "weights must be (levels, Cout, Cin, 3, 3, 3)");
+    TORCH_CHECK(input.size(1) == weights.size(2), "input tensor shape does not match weights tensor");
+    TORCH_CHECK(input.scalar_type() == torch::kFloat32 && weights.scalar_type() == torch::kFloat32, "the tensor-core path takes float32 tensors");
+    c10::cuda::CUDAGuard guard(input.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    const int64_t cin = input.size(1), cout = weights.size(1), n = input.size(2);
+    int64_t max_tree = 1, rows_bytes = 256, w_bytes = 256;
+    for (size_t i = 0; i < aprs.size(); ++i) {
+        check_level_delta(*aprs[i], dl[i]);
+        aprnet_apr* h = aprs[i]->handle(input);
+        TORCH_CHECK(aprs[i]->number_parts(dl[i]) <= n, "input has fewer particles than the APR at this level delta");
+        max_tree = std::max<int64_t>(max_tree, aprnet_tree_size(h, dl[i]));
+        const int64_t rb = aprnet_conv333_tc_packed_rows_bytes(h, dl[i], (int) cin);
+        rows_bytes = std::max(rows_bytes, rb);
+        w_bytes = std::max(w_bytes, aprnet_conv333_tc_forward_workspace_bytes(h, dl[i], (int) cin, (int) cout, (int) weights.size(0)) - rb);
+    }
+    auto output = torch::empty({input.size(0), cout, n}, input.options());
+    auto tree = torch::empty({cin, max_tree}, input.options());
+    // per batch item: [packed rows | packed weights]; only the rows part is handed back (the view keeps the buffer)
+    auto ws = torch::empty({input.size(0), rows_bytes + w_bytes}, input.options().dtype(torch::kUInt8));
+    for (int64_t b = 0; b < input.size(0); ++b) {
+        check(aprnet_conv333_forward_tc(aprs[b]->handle(input), dl[b], (int) cin, (int) cout, (int) weights.size(0), (const float*) row(input, b), n,
+                                        (const float*) weights.data_ptr(), (float*) row(output, b), n, (float*) tree.data_ptr(), max_tree,
+                                        row(ws, b), stream_of(input)), "conv333_forward (tensor cores)");
+        zero_padding(output, b, aprs[b]->number_parts(dl[b]));
+    }
+    return {output, ws};
+}
+
+std::vector<torch::Tensor> conv333_backward_with_rows(std::vector<APR*>& aprs, torch::Tensor rows, torch::Tensor weights, torch::Tensor grad_output,
+                                                      torch::Tensor level_delta, bool need_grad_input) {
+    CHECK_INPUT(weights); CHECK_INPUT(grad_output); CHECK_INPUT(rows);
+    check_batch(aprs, grad_output);
+    TORCH_CHECK(rows.dim() == 2 && rows.size(0) == grad_output.size(0) && rows.scalar_type() == torch::kUInt8, "rows must be the (batch, bytes) buffer of conv333_forward_keep_rows");
+    TORCH_CHECK(grad_output.dim() == 3 && grad_output.size(1) == weights.size(1) && grad_output.scalar_type() == torch::kFloat32, "grad_output shape does not match");
+    c10::cuda::CUDAGuard guard(grad_output.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    const int64_t cin = weights.size(2), cout = weights.size(1), n = grad_output.size(2);
+    int64_t max_tree = 1, bytes = 256;
+    for (size_t i = 0; i < aprs.size(); ++i) {
+        check_level_delta(*aprs[i], dl[i]);
+        aprnet_apr* h = aprs[i]->handle(grad_output);
+        max_tree = std::max<int64_t>(max_tree, aprnet_tree_size(h, dl[i]));
+        TORCH_CHECK(rows.size(1) >= aprnet_conv333_tc_packed_rows_bytes(h, dl[i], (int) cin), "rows buffer too small for this APR");
+        bytes = std::max<int64_t>(bytes, aprnet_conv333_tc_workspace_bytes(h, dl[i], (int) cin, (int) cout, (int) weights.size(0)));
+    }
+    auto grad_tree = torch::empty({cin, max_tree}, grad_output.options());
+    auto grad_input = need_grad_input ? torch::empty({grad_output.size(0), cin, n}, grad_output.options()) : torch::Tensor();
+    auto grad_weights = torch::zeros_like(weights);
+    auto ws = torch::empty({bytes}, grad_output.options().dtype(torch::kUInt8));
+    auto partial = torch::empty({aprnet_conv333_tc_dw_partial_elems((int) cin, (int) cout)}, grad_output.options());
+    for (int64_t b = 0; b < grad_output.size(0); ++b) {
+        check(aprnet_conv333_backward_tc_rows(aprs[b]->handle(grad_output), dl[b], (int) cin, (int) cout, (int) weights.size(0), row(rows, b),
+                                              (const float*) row(grad_output, b), n, (const float*) weights.data_ptr(),
+                                              need_grad_input ? (float*) row(grad_input, b) : nullptr, n, (float*) grad_weights.data_ptr(),
+                                              (float*) grad_tree.data_ptr(), max_tree, (float*) partial.data_ptr(), ws.data_ptr(), stream_of(grad_output)),
+              "conv333_backward (tensor cores, packed rows)");
+        if (need_grad_input) zero_padding(grad_input, b, aprs[b]->number_parts(dl[b]));
+    }
+    return {grad_input, grad_weights};
+}
+
 static std::vector<torch::Tensor> conv333_backward_impl(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights,
                                             torch::Tensor grad_output, torch::Tensor level_delta, c10::optional<torch::Tensor> saved_tree,
                                             bool need_grad_input = true) {
@@ -691,6 +758,8 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
     // extensions: keep the tree means of the forward pass for the backward pass
     cuda.def("conv333_forward_keep_tree", &conv333_forward_keep_tree, "aprs"_a, "input"_a, "weights"_a, "level_delta"_a);
     cuda.def("conv333_backward_with_tree", &conv333_backward_with_tree, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a, "tree"_a, "need_grad_input"_a = true);
+    cuda.def("conv333_forward_keep_rows", &conv333_forward_keep_rows, "aprs"_a, "input"_a, "weights"_a, "level_delta"_a);
+    cuda.def("conv333_backward_with_rows", &conv333_backward_with_rows, "aprs"_a, "rows"_a, "weights"_a, "grad_output"_a, "level_delta"_a, "need_grad_input"_a = true);
     cuda.def("upsample_const_forward", &upsample_const_forward, "aprs"_a, "input"_a, "level_delta"_a);
     cuda.def("upsample_const_backward", &upsample_const_backward, "aprs"_a, "grad_output"_a, "level_delta"_a);
     cuda.def("reconstruct_forward", &reconstruct_forward, "aprs"_a, "input"_a, "level_delta"_a);

@@ -598,10 +598,42 @@ extern "C" int aprnet_conv333_forward_tc(aprnet_apr* a, int dl, int cin, int cou
     return aprnet_tc_gather_conv(a, dl, 0, cin, cout, slots, rows, kpad, n, n + t, w, wp, out, ld_out, st);
 }
 
-// Complete backward pass of the 3x3x3 convolution with the contractions on the tensor cores:
-// grad_weights (accumulated into), grad_input (written; float32 (Cin, ld_in); may be null: skipped).
-//   tree means -> packed input rows, packed dO rows -> weight gradient (tcgen05, deterministic)
-//   -> same-level input gradient (tcgen05 gather) -> cross-level part (atomicAdd) + tree adjoint.
+// Backward pass of the 3x3x3 convolution with the contractions on the tensor cores, from the packed
+// bf16 rows of the input that the forward call left at the start of its workspace
+// (aprnet_conv333_tc_packed_rows_bytes() bytes: particles, tree means, zero row): nothing of the fp32 input
+// is needed.  grad_weights is accumulated into, grad_input (float32 (Cin, ld_in)) written; null: skipped.
+//   packed dO rows -> weight gradient (tcgen05, deterministic) -> same-level input gradient (tcgen05 gather)
+//   -> cross-level part (per-(target, tap) sums + gather over the targets) and tree adjoint.
+// workspace: aprnet_conv333_tc_workspace_bytes() bytes (its leading part is not touched, so the forward
+// workspace itself may be passed as packed_input_rows).
+extern "C" int aprnet_conv333_backward_tc_rows(aprnet_apr* a, int dl, int cin, int cout, int slots, const void* packed_input_rows,
+                                               const float* gout, int64_t ld_out, const float* w, float* gin, int64_t ld_in, float* gw,
+                                               float* gtree, int64_t ld_tree, float* partial, void* workspace, void* stream) {
+    APRNET_ARG_CHECK(a && a->valid_dl(dl) && cin > 0 && cout > 0 && slots > 0 && packed_input_rows && gout && w && gw && gtree && partial && workspace, "bad argument");
+    APRNET_ARG_CHECK(ld_out >= a->number_parts(dl) && (!gin || ld_in >= a->number_parts(dl)) && ld_tree >= a->tree_size(dl), "leading dimension too small");
+    cudaStream_t st = (cudaStream_t) stream;
+    const ll n = a->number_parts(dl), t = a->tree_size(dl);
+    const int xpad = aprnet_tc_pad(cin), gpad = aprnet_tc_pad(cout);
+    char* ws = (char*) workspace;
+    void* grows = ws + aprnet_tc_rows_bytes(n + t + 1, cin);
+    void* wp = (char*) grows + aprnet_tc_rows_bytes(n + 1, cout);
+    int rc;
+    if ((rc = aprnet_tc_pack_rows(gout, ld_out, n, nullptr, 0, 0, cout, gpad, grows, st))) return rc;
+    if ((rc = aprnet_conv333_backward_weights_tc(a, dl, cin, cout, slots, packed_input_rows, xpad, grows, gpad, gw, partial, st))) return rc;
+    if (!gin) return APRNET_OK;          // the caller does not need the input gradient (first layer of a network)
+    if ((rc = aprnet_tc_gather_conv(a, dl, 1, cin, cout, slots, grows, gpad, n, n, w, wp, gin, ld_in, st))) return rc;
+    void* edge_ws = (char*) wp + aprnet_tc_weight_bytes(cout, cin, slots);
+    return aprnet_conv333_backward_input_cross_level_tc(a, dl, cin, cout, slots, grows, gpad, w, gin, ld_in, gtree, ld_tree, wp, edge_ws,
+                                                        aprnet_edge_workspace_bytes(a, dl, cout), st);
+}
+
+extern "C" int64_t aprnet_conv333_tc_packed_rows_bytes(const aprnet_apr* a, int dl, int cin) {
+    if (!a || !a->valid_dl(dl)) return -1;
+    return (int64_t) aprnet_tc_rows_bytes(a->number_parts(dl) + a->tree_size(dl) + 1, cin);
+}
+
+// Complete backward pass from the fp32 input: fills the tree means (unless tree_valid), packs the input
+// rows into the workspace and continues as aprnet_conv333_backward_tc_rows.
 extern "C" int aprnet_conv333_backward_tc(aprnet_apr* a, int dl, int cin, int cout, int slots, const float* in, int64_t ld_in,
                                           const float* gout, int64_t ld_out, const float* w, float* gin, float* gw,
                                           float* tree, int tree_valid, float* gtree, int64_t ld_tree, float* partial,
@@ -612,18 +644,6 @@ extern "C" int aprnet_conv333_backward_tc(aprnet_apr* a, int dl, int cin, int co
     int rc = tree_valid ? APRNET_OK : aprnet_fill_tree_mean_forward(a, dl, APRNET_F32, cin, in, ld_in, tree, ld_tree, st);
     if (rc) return rc;
     const ll n = a->number_parts(dl), t = a->tree_size(dl);
-    const int xpad = aprnet_tc_pad(cin), gpad = aprnet_tc_pad(cout);
-    char* ws = (char*) workspace;
-    void* xrows = ws;
-    void* grows = ws + aprnet_tc_rows_bytes(n + t + 1, cin);
-    void* wp = (char*) grows + aprnet_tc_rows_bytes(n + 1, cout);
-    if ((rc = aprnet_tc_pack_rows(in, ld_in, n, tree, ld_tree, t, cin, xpad, xrows, st))) return rc;
-    if ((rc = aprnet_tc_pack_rows(gout, ld_out, n, nullptr, 0, 0, cout, gpad, grows, st))) return rc;
-    if ((rc = aprnet_conv333_backward_weights_tc(a, dl, cin, cout, slots, xrows, xpad, grows, gpad, gw, partial, st))) return rc;
-    if (!gin) return APRNET_OK;          // the caller does not need the input gradient (first layer of a network)
-    if ((rc = aprnet_tc_gather_conv(a, dl, 1, cin, cout, slots, grows, gpad, n, n, w, wp, gin, ld_in, st))) return rc;
-    void* edge_ws = (char*) wp + aprnet_tc_weight_bytes(cout, cin, slots);
-    return aprnet_conv333_backward_input_cross_level_tc(a, dl, cin, cout, slots, grows, gpad, w, gin, ld_in, gtree, ld_tree, wp, edge_ws,
-                                                        aprnet_edge_workspace_bytes(a, dl, cout), st);
+    if ((rc = aprnet_tc_pack_rows(in, ld_in, n, tree, ld_tree, t, cin, aprnet_tc_pad(cin), workspace, st))) return rc;
+    return aprnet_conv333_backward_tc_rows(a, dl, cin, cout, slots, workspace, gout, ld_out, w, gin, ld_in, gw, gtree, ld_tree, partial, workspace, stream);
 }
-

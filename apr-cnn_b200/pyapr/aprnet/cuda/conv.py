@@ -12,7 +12,8 @@ from torch.autograd import Function
 from torch.nn import init
 
 from _pyaprwrapper.data_containers import APRPtrVector
-from _pyaprwrapper.aprnet.cuda import (conv111_backward, conv111_forward, conv333_backward_with_tree, conv333_forward_keep_tree,
+from _pyaprwrapper.aprnet.cuda import (conv111_backward, conv111_forward, conv333_backward_with_rows, conv333_backward_with_tree,
+                                       conv333_forward_keep_rows, conv333_forward_keep_tree, get_conv_precision,
                                        restrict_kernel333_backward, restrict_kernel333_forward)
 
 
@@ -25,18 +26,33 @@ class Conv333Function(Function):
         expanded = restrict_kernel333_forward(weights, num_levels)
         ctx.aprs = aprs
         ctx.num_stencils = weights.shape[0]
-        # the tree means computed by the forward pass are kept (1/7 of the input's size) so that the
-        # backward pass does not have to fill the tree again
-        out, tree = conv333_forward_keep_tree(APRPtrVector(aprs), inputs, expanded, level_deltas)
-        ctx.save_for_backward(inputs, expanded, bias, level_deltas.clone(), tree)
+        ctx.packed = get_conv_precision() == "bf16" and inputs.dtype == torch.float32
+        if ctx.packed:
+            # tensor-core path: the backward pass works from the packed bf16 rows of the input (particles + tree
+            # means) that the forward pass produced anyway; they replace the fp32 input among the saved tensors
+            # (half the bytes) and spare the backward pass the tree fill and the packing
+            out, rows = conv333_forward_keep_rows(APRPtrVector(aprs), inputs, expanded, level_deltas)
+            ctx.save_for_backward(expanded, bias, level_deltas.clone(), rows)
+        else:
+            # the tree means computed by the forward pass are kept (1/7 of the input's size) so that the
+            # backward pass does not have to fill the tree again
+            out, tree = conv333_forward_keep_tree(APRPtrVector(aprs), inputs, expanded, level_deltas)
+            ctx.save_for_backward(inputs, expanded, bias, level_deltas.clone(), tree)
         if bias is not None:
             out = out + bias.view(1, -1, 1)
         return out
 
     @staticmethod
     def backward(ctx, grad_output):
-        inputs, expanded, bias, level_deltas, tree = ctx.saved_tensors
         grad_output = grad_output.contiguous()
+        if ctx.packed:
+            expanded, bias, level_deltas, rows = ctx.saved_tensors
+            grad_input, grad_expanded = conv333_backward_with_rows(APRPtrVector(ctx.aprs), rows, expanded, grad_output, level_deltas,
+                                                                   bool(ctx.needs_input_grad[0]))
+            grad_weights = restrict_kernel333_backward(grad_expanded, ctx.num_stencils)
+            grad_bias = grad_output.sum(dim=(0, 2)) if bias is not None else None
+            return grad_input, grad_weights, grad_bias, None, None
+        inputs, expanded, bias, level_deltas, tree = ctx.saved_tensors
         # the input gradient of a first layer (features that do not require grad) is not computed
         grad_input, grad_expanded = conv333_backward_with_tree(APRPtrVector(ctx.aprs), inputs, expanded, grad_output, level_deltas, tree,
                                                                bool(ctx.needs_input_grad[0]))

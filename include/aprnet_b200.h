@@ -152,6 +152,14 @@ int aprnet_conv333_backward_tc(aprnet_apr* apr, int level_delta, int cin, int co
                                const float* weights, float* grad_input, float* grad_weights,
                                float* tree_scratch, int tree_scratch_is_valid, float* grad_tree_scratch, int64_t ld_tree,
                                float* partial, void* workspace, void* stream);
+/* The same backward pass from the packed bf16 rows of the input that aprnet_conv333_forward_tc left in
+ * the first aprnet_conv333_tc_packed_rows_bytes() bytes of its workspace (keep that buffer instead of the
+ * fp32 input and the tree means: half the bytes, and no second packing pass).  grad_input may be NULL. */
+int64_t aprnet_conv333_tc_packed_rows_bytes(const aprnet_apr* apr, int level_delta, int cin);
+int aprnet_conv333_backward_tc_rows(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
+                                    const void* packed_input_rows, const float* grad_output, int64_t ld_out,
+                                    const float* weights, float* grad_input, int64_t ld_in, float* grad_weights,
+                                    float* grad_tree_scratch, int64_t ld_tree, float* partial, void* workspace, void* stream);
 /* Building blocks of the above, exported for callers that keep the packed copies around. */
 int aprnet_conv333_backward_weights_tc(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
                                        const void* packed_input_rows, int input_row_width,
