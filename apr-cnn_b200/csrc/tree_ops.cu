@@ -11,8 +11,14 @@
 namespace {
 
 typedef long long ll;
-constexpr int TPB = 256;
-constexpr int CH_PER_BLOCK = 8;
+#ifndef APRNET_TREE_TPB
+#define APRNET_TREE_TPB 256
+#endif
+#ifndef APRNET_TREE_CH
+#define APRNET_TREE_CH 8
+#endif
+constexpr int TPB = APRNET_TREE_TPB;
+constexpr int CH_PER_BLOCK = APRNET_TREE_CH;
 
 template<typename T> struct DT;
 template<> struct DT<float> { static constexpr int id = APRNET_F32; };
@@ -21,40 +27,45 @@ template<> struct DT<double> { static constexpr int id = APRNET_F64; };
 // parent level lp: tree[t] = scale[t] * sum(children).  All child values of the block's channels are
 // requested before any is used (CH_PER_BLOCK x 8 independent loads in flight per thread).
 template<typename T>
-__global__ void tree_mean_level_kernel(const int32_t* __restrict__ child, const float* __restrict__ scale, ll n_tree,
+__global__ void __launch_bounds__(TPB) tree_mean_level_kernel(const int32_t* __restrict__ child, const float* __restrict__ scale, ll n_tree,
                                        ll tb, ll te, const T* __restrict__ in, ll ld_in, T* __restrict__ tree,
                                        ll ld_tree, int C, ll up_off, int use_up) {
     const ll t = tb + (ll) blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= te) return;
-    // resolve the eight child slots to (pointer base, offset) once
-    ll off[8];
-    bool from_tree[8], present[8], coded[8];
+    // resolve the eight child slots once: pointer to the child's value in channel c0 and the channel stride
+    const int c0 = blockIdx.y * CH_PER_BLOCK;
+    const T* src[8];
+    unsigned coded = 0;                 // slots whose child is a tree node (summed after the particles)
+    const unsigned in_tree = use_up ? 0u : 0xffu;      // coded children live in the tree scratch unless they are upgraded nodes
 #pragma unroll
     for (int s = 0; s < 8; ++s) {
         const int32_t v = child[(ll) s * n_tree + t];
-        present[s] = v != APRNET_NONE;
-        coded[s] = v < APRNET_NONE;
-        from_tree[s] = v < APRNET_NONE && !use_up;
-        off[s] = v >= 0 ? (ll) v : (v == APRNET_NONE ? 0 : aprnet_dec_tree(v) + (use_up ? up_off : 0));
+        src[s] = nullptr;
+        if (v >= 0) src[s] = in + (ll) c0 * ld_in + v;
+        else if (v != APRNET_NONE) {
+            coded |= 1u << s;
+            src[s] = use_up ? in + (ll) c0 * ld_in + aprnet_dec_tree(v) + up_off : tree + (ll) c0 * ld_tree + aprnet_dec_tree(v);
+        }
     }
     const T f = (T) scale[t];
-    const int c0 = blockIdx.y * CH_PER_BLOCK;
+    const int nch = min(CH_PER_BLOCK, C - c0);
     T vals[CH_PER_BLOCK][8];
 #pragma unroll
     for (int k = 0; k < CH_PER_BLOCK; ++k) {
-        const int c = min(c0 + k, C - 1);
-        const T* x = in + (ll) c * ld_in;
-        const T* tr = tree + (ll) c * ld_tree;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) vals[k][s] = present[s] ? (from_tree[s] ? tr[off[s]] : x[off[s]]) : T(0);
+        for (int s = 0; s < 8; ++s) {
+            vals[k][s] = (src[s] && k < nch) ? *src[s] : T(0);
+            src[s] += (coded & in_tree) >> s & 1 ? ld_tree : ld_in;
+        }
     }
+    T* dst = tree + (ll) c0 * ld_tree + t;
 #pragma unroll
     for (int k = 0; k < CH_PER_BLOCK; ++k) {
-        if (c0 + k >= C) break;
+        if (k >= nch) break;
         T s_part = 0, s_tree = 0;       // particles first, then tree children (fixed order)
 #pragma unroll
-        for (int s = 0; s < 8; ++s) { if (coded[s]) s_tree += vals[k][s]; else s_part += vals[k][s]; }
-        tree[(ll) (c0 + k) * ld_tree + t] = f * (s_part + s_tree);
+        for (int s = 0; s < 8; ++s) { if (coded >> s & 1) s_tree += vals[k][s]; else s_part += vals[k][s]; }
+        dst[(ll) k * ld_tree] = f * (s_part + s_tree);
     }
 }
 
