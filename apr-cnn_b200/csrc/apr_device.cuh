@@ -135,6 +135,13 @@ void aprnet_free_edge_plan(EdgePlan& ep);
 int aprnet_tc_gather_targets(aprnet_apr* a, int dl, int cin, int cout, int slots, const void* vrows, int gpad, long long zero_row,
                              const void* wp_packed, const EdgePlan* ep, long long a0, long long a1,
                              float* gin, long long ld_in, float* gtree, long long ld_tree, cudaStream_t st);
+// CUDA-core fp32 kernels for Cin <= 4 (conv333_small.cu), used by the tensor-core drivers for such layers:
+// vals = channel-major staging buffer [cin][N + T + 1] (particles, tree means, zero)
+bool aprnet_small_cin(int cin);
+int aprnet_small_stage(const float* x, long long ld_x, long long n, const float* tree, long long ld_tree, long long t, int cin, float* vals, cudaStream_t st);
+int aprnet_small_forward(aprnet_apr* a, int dl, int cin, int cout, int slots, const float* vals, const float* w, float* out, long long ld_out, cudaStream_t st);
+int aprnet_small_backward_weights(aprnet_apr* a, int dl, int cin, int cout, int slots, const float* vals, const float* gout, long long ld_out,
+                                  float* gw, float* partial, cudaStream_t st);
 int aprnet_tc_pack_weights(const float* w, int slots, int cin, int cout, int mode, void* wp, cudaStream_t st);
 size_t aprnet_tc_weight_bytes(int k_dim, int n_dim, int slots);
 size_t aprnet_tc_rows_bytes(long long rows, int channels);

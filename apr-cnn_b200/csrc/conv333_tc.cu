@@ -593,6 +593,10 @@ extern "C" int aprnet_conv333_forward_tc(aprnet_apr* a, int dl, int cin, int cou
     char* ws = (char*) workspace;
     void* rows = ws;
     void* wp = ws + aprnet_tc_rows_bytes(n + t + 1, cin);
+    if (aprnet_small_cin(cin)) {         // first-layer widths: fp32 CUDA-core kernels; the rows area holds the fp32 staging buffer instead
+        if ((rc = aprnet_small_stage(in, ld_in, n, tree, ld_tree, t, cin, (float*) rows, st))) return rc;
+        return aprnet_small_forward(a, dl, cin, cout, slots, (const float*) rows, w, out, ld_out, st);
+    }
     rc = aprnet_tc_pack_rows(in, ld_in, n, tree, ld_tree, t, cin, kpad, rows, st);
     if (rc) return rc;
     return aprnet_tc_gather_conv(a, dl, 0, cin, cout, slots, rows, kpad, n, n + t, w, wp, out, ld_out, st);
@@ -600,8 +604,8 @@ extern "C" int aprnet_conv333_forward_tc(aprnet_apr* a, int dl, int cin, int cou
 
 // Backward pass of the 3x3x3 convolution with the contractions on the tensor cores, from the packed
 // bf16 rows of the input that the forward call left at the start of its workspace
-// (aprnet_conv333_tc_packed_rows_bytes() bytes: particles, tree means, zero row): nothing of the fp32 input
-// is needed.  grad_weights is accumulated into, grad_input (float32 (Cin, ld_in)) written; null: skipped.
+// (aprnet_conv333_tc_packed_rows_bytes() bytes: particles, tree means, zero row; for Cin <= 4 the same
+// area holds an fp32 channel-major copy instead, see conv333_small.cu): nothing of the fp32 input is needed.  grad_weights is accumulated into, grad_input (float32 (Cin, ld_in)) written; null: skipped.
 //   packed dO rows -> weight gradient (tcgen05, deterministic) -> same-level input gradient (tcgen05 gather)
 //   -> cross-level part (per-(target, tap) sums + gather over the targets) and tree adjoint.
 // workspace: aprnet_conv333_tc_workspace_bytes() bytes (its leading part is not touched, so the forward
@@ -618,8 +622,10 @@ extern "C" int aprnet_conv333_backward_tc_rows(aprnet_apr* a, int dl, int cin, i
     void* grows = ws + aprnet_tc_rows_bytes(n + t + 1, cin);
     void* wp = (char*) grows + aprnet_tc_rows_bytes(n + 1, cout);
     int rc;
-    if ((rc = aprnet_tc_pack_rows(gout, ld_out, n, nullptr, 0, 0, cout, gpad, grows, st))) return rc;
-    if ((rc = aprnet_conv333_backward_weights_tc(a, dl, cin, cout, slots, packed_input_rows, xpad, grows, gpad, gw, partial, st))) return rc;
+    if (!(aprnet_small_cin(cin) && !gin) && (rc = aprnet_tc_pack_rows(gout, ld_out, n, nullptr, 0, 0, cout, gpad, grows, st))) return rc;
+    if (aprnet_small_cin(cin)) {
+        if ((rc = aprnet_small_backward_weights(a, dl, cin, cout, slots, (const float*) packed_input_rows, gout, ld_out, gw, partial, st))) return rc;
+    } else if ((rc = aprnet_conv333_backward_weights_tc(a, dl, cin, cout, slots, packed_input_rows, xpad, grows, gpad, gw, partial, st))) return rc;
     if (!gin) return APRNET_OK;          // the caller does not need the input gradient (first layer of a network)
     if ((rc = aprnet_tc_gather_conv(a, dl, 1, cin, cout, slots, grows, gpad, n, n, w, wp, gin, ld_in, st))) return rc;
     void* edge_ws = (char*) wp + aprnet_tc_weight_bytes(cout, cin, slots);
@@ -644,6 +650,7 @@ extern "C" int aprnet_conv333_backward_tc(aprnet_apr* a, int dl, int cin, int co
     int rc = tree_valid ? APRNET_OK : aprnet_fill_tree_mean_forward(a, dl, APRNET_F32, cin, in, ld_in, tree, ld_tree, st);
     if (rc) return rc;
     const ll n = a->number_parts(dl), t = a->tree_size(dl);
-    if ((rc = aprnet_tc_pack_rows(in, ld_in, n, tree, ld_tree, t, cin, aprnet_tc_pad(cin), workspace, st))) return rc;
+    if (aprnet_small_cin(cin)) { if ((rc = aprnet_small_stage(in, ld_in, n, tree, ld_tree, t, cin, (float*) workspace, st))) return rc; }
+    else if ((rc = aprnet_tc_pack_rows(in, ld_in, n, tree, ld_tree, t, cin, aprnet_tc_pad(cin), workspace, st))) return rc;
     return aprnet_conv333_backward_tc_rows(a, dl, cin, cout, slots, workspace, gout, ld_out, w, gin, ld_in, gw, gtree, ld_tree, partial, workspace, stream);
 }
