@@ -30,8 +30,14 @@ constexpr int DW_THREADS = 9 * 32;            // 8 producer warps + 1 MMA warp
 constexpr int DW_MAX_STAGES = 6;
 constexpr int A_STAGE = 2 * PT * 128;         // 128 accumulator rows = two 64-element swizzle atoms per particle
 
+constexpr int DW_MAX_SEGS = APRNET_MAX_LEVELS;
 struct DwParams {
-    ll seg_begin, seg_end, range_len;      // output locations [seg_begin, seg_end) split into ranges of range_len
+    // the levels of the level delta, each split into ranges of range_len locations; range r belongs to the
+    // level i with range_first[i] <= r < range_first[i + 1]
+    int n_segs;
+    ll seg_begin[DW_MAX_SEGS], seg_end[DW_MAX_SEGS];
+    int range_first[DW_MAX_SEGS + 1];
+    ll range_len;
     const int32_t* nbr; ll N;
     const __nv_bfloat16* xrows; int xpad;  // packed inputs [N + T + 1][xpad]; tree rows start at tree_base, zeros at zero_row
     ll tree_base, zero_row;
@@ -68,8 +74,10 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
     const int tap0 = grp * P.taps_per_group;
     const int ntaps = min(P.taps_per_group, 27 - tap0);
     const int MT = (ntaps + TPT - 1) / TPT;             // accumulator tiles of this block
-    const ll pb = P.seg_begin + (ll) blockIdx.x * P.range_len;
-    const ll pe = min(P.seg_end, pb + P.range_len);
+    int seg = 0;
+    while (seg + 1 < P.n_segs && (int) blockIdx.x >= P.range_first[seg + 1]) ++seg;
+    const ll pb = P.seg_begin[seg] + (ll) ((int) blockIdx.x - P.range_first[seg]) * P.range_len;
+    const ll pe = min(P.seg_end[seg], pb + P.range_len);
     const int nchunks = pe > pb ? (int) ((pe - pb + PT - 1) / PT) : 0;
     const int total_stages = nchunks * MT;
     const int gpiece = min(256, P.gpad - cob * 256);    // dO channels of this block
@@ -257,7 +265,7 @@ int launch_dw(const DwParams& P, int nranges, int blocks_y, cudaStream_t st, con
 
 extern "C" int64_t aprnet_conv333_tc_dw_partial_elems(int cin, int cout) {
     const ll per = (ll) 27 * cin * cout;
-    const ll ranges = std::max<ll>(8, std::min<ll>(1024, (64ll << 20) / per));
+    const ll ranges = std::max<ll>(32, std::min<ll>(1024, (64ll << 20) / per));     // at least one per level plus room for a wave
     return (int64_t) (ranges * per);
 }
 
@@ -289,33 +297,45 @@ extern "C" int aprnet_conv333_backward_weights_tc(aprnet_apr* a, int dl, int cin
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     char pname[64];
     snprintf(pname, sizeof(pname), "conv333_tc_dw:ci%d:co%d:dl%d", cin, cout, dl);
-    for (const Segment& s : aprnet_segments(a, dl, slots, false)) {
-        const ll len = s.end - s.begin;
-        // one block per SM at a time: enough ranges for two waves, each at least 4 chunks long
-        ll want = std::max<ll>(1, ((ll) 2 * sms + blocks_y - 1) / blocks_y);
-        want = std::min<ll>(want, (len + 4 * PT - 1) / (4 * PT));
-        const int nranges = (int) std::max<ll>(1, std::min<ll>(max_ranges, want));
-        DwParams P;
-        P.seg_begin = s.begin; P.seg_end = s.end;
-        P.range_len = ((len + nranges - 1) / nranges + PT - 1) / PT * PT;
-        P.nbr = plan->nbr; P.N = n;
-        P.xrows = (const __nv_bfloat16*) xrows; P.xpad = xpad; P.tree_base = n; P.zero_row = n + t;
-        P.grows = (const __nv_bfloat16*) grows; P.gpad = gpad; P.g_zero_row = n;
-        P.partial = partial; P.cin = cin; P.cout = cout; P.ci_blocks = ci_blocks; P.groups = groups; P.taps_per_group = taps_per_group;
-        P.error_flag = aprnet_tc_error_flag_device();
-        int rc;
-#define DW_CASE(CIB_, NCOL_) if (cibk == CIB_ && ncol == NCOL_) rc = launch_dw<CIB_, NCOL_>(P, nranges, blocks_y, st, pname); else
-        DW_CASE(16, 64) DW_CASE(16, 128) DW_CASE(16, 192) DW_CASE(16, 256)
-        DW_CASE(32, 64) DW_CASE(32, 128) DW_CASE(32, 192) DW_CASE(32, 256)
-        DW_CASE(64, 64) DW_CASE(64, 128) DW_CASE(64, 192) DW_CASE(64, 256)
-        DW_CASE(128, 64) DW_CASE(128, 128) DW_CASE(128, 192) DW_CASE(128, 256)
-        { aprnet_set_error("conv333 tensor-core weight gradient: unsupported blocking"); return APRNET_ERR_UNSUPPORTED; }
-#undef DW_CASE
-        if (rc) return rc;
-        { AprnetProfScope _prof("conv333_dw_reduce", st);
-        reduce_partial_kernel<float><<<aprnet_ceil_div(elems, 256), 256, 0, st>>>(partial, nranges, elems, gw + (ll) s.slot * elems);
-        }
-        APRNET_LAUNCH_CHECK();
+    // one launch over all levels: ranges of equal length, enough of them for two waves of one block per SM,
+    // each at least 4 chunks long; a level's ranges are summed into the slot of that level afterwards
+    const std::vector<Segment> segs = aprnet_segments(a, dl, slots, false);
+    ll total_len = 0;
+    for (const Segment& sg : segs) total_len += sg.end - sg.begin;
+    if (total_len == 0) return APRNET_OK;
+    ll want = std::max<ll>(1, ((ll) 2 * sms + blocks_y - 1) / blocks_y);
+    want = std::min<ll>(want, (total_len + 4 * PT - 1) / (4 * PT));
+    want = std::max<ll>(1, std::min<ll>(max_ranges - (ll) segs.size(), want));
+    DwParams P;
+    P.range_len = ((total_len + want - 1) / want + PT - 1) / PT * PT;
+    P.n_segs = (int) segs.size();
+    P.range_first[0] = 0;
+    for (int i = 0; i < P.n_segs; ++i) {
+        P.seg_begin[i] = segs[i].begin; P.seg_end[i] = segs[i].end;
+        P.range_first[i + 1] = P.range_first[i] + (int) ((segs[i].end - segs[i].begin + P.range_len - 1) / P.range_len);
     }
+    const int nranges = P.range_first[P.n_segs];
+    if (nranges > max_ranges) { aprnet_set_error("conv333 tensor-core weight gradient: %d ranges exceed the partial buffer", nranges); return APRNET_ERR_ARG; }
+    P.nbr = plan->nbr; P.N = n;
+    P.xrows = (const __nv_bfloat16*) xrows; P.xpad = xpad; P.tree_base = n; P.zero_row = n + t;
+    P.grows = (const __nv_bfloat16*) grows; P.gpad = gpad; P.g_zero_row = n;
+    P.partial = partial; P.cin = cin; P.cout = cout; P.ci_blocks = ci_blocks; P.groups = groups; P.taps_per_group = taps_per_group;
+    P.error_flag = aprnet_tc_error_flag_device();
+    int rc;
+#define DW_CASE(CIB_, NCOL_) if (cibk == CIB_ && ncol == NCOL_) rc = launch_dw<CIB_, NCOL_>(P, nranges, blocks_y, st, pname); else
+    DW_CASE(16, 64) DW_CASE(16, 128) DW_CASE(16, 192) DW_CASE(16, 256)
+    DW_CASE(32, 64) DW_CASE(32, 128) DW_CASE(32, 192) DW_CASE(32, 256)
+    DW_CASE(64, 64) DW_CASE(64, 128) DW_CASE(64, 192) DW_CASE(64, 256)
+    DW_CASE(128, 64) DW_CASE(128, 128) DW_CASE(128, 192) DW_CASE(128, 256)
+    { aprnet_set_error("conv333 tensor-core weight gradient: unsupported blocking"); return APRNET_ERR_UNSUPPORTED; }
+#undef DW_CASE
+    if (rc) return rc;
+    for (int i = 0; i < P.n_segs; ++i) {
+        const int cnt = P.range_first[i + 1] - P.range_first[i];
+        if (cnt == 0) continue;
+        AprnetProfScope _prof("conv333_dw_reduce", st);
+        reduce_partial_kernel<float><<<aprnet_ceil_div(elems, 256), 256, 0, st>>>(partial + (ll) P.range_first[i] * elems, cnt, elems, gw + (ll) segs[i].slot * elems);
+    }
+    APRNET_LAUNCH_CHECK();
     return APRNET_OK;
 }
