@@ -20,6 +20,7 @@
 #include "tc_ptx.cuh"
 #include <cuda_bf16.h>
 #include <algorithm>
+#include <cstdlib>
 
 namespace {
 
@@ -303,7 +304,9 @@ extern "C" int aprnet_conv333_backward_weights_tc(aprnet_apr* a, int dl, int cin
     ll total_len = 0;
     for (const Segment& sg : segs) total_len += sg.end - sg.begin;
     if (total_len == 0) return APRNET_OK;
-    ll want = std::max<ll>(1, ((ll) 2 * sms + blocks_y - 1) / blocks_y);
+    int waves = 2;
+    if (const char* e = getenv("APRNET_DW_WAVES")) waves = std::max(1, atoi(e));
+    ll want = std::max<ll>(1, ((ll) waves * sms + blocks_y - 1) / blocks_y);
     want = std::min<ll>(want, (total_len + 4 * PT - 1) / (4 * PT));
     want = std::max<ll>(1, std::min<ll>(max_ranges - (ll) segs.size(), want));
     DwParams P;
