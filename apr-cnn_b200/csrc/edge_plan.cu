@@ -135,11 +135,20 @@ __global__ void vrow_reduce_kernel(const int32_t* __restrict__ vstart, const int
     const ll v = v0 + e / nch;
     const int c = (int) (e % nch);
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int i = vstart[v]; i < vstart[v + 1]; ++i) {
-        const uint4 q = __ldg(reinterpret_cast<const uint4*>(grows + (ll) vsrc[i] * gpad + c * 8));
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+    const int e1 = vstart[v + 1];
+    for (int i = vstart[v]; i < e1; i += 4) {          // four rows requested before any is added (runs are 1-4 rows long)
+        int32_t src[4];
+        uint4 q[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) { const float2 f = __bfloat1622float2(h[k]); acc[2 * k] += f.x; acc[2 * k + 1] += f.y; }
+        for (int u = 0; u < 4; ++u) src[u] = i + u < e1 ? __ldg(vsrc + i + u) : -1;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) q[u] = src[u] >= 0 ? __ldg(reinterpret_cast<const uint4*>(grows + (ll) src[u] * gpad + c * 8)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {                   // ascending location order
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q[u]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { const float2 f = __bfloat1622float2(h[k]); acc[2 * k] += f.x; acc[2 * k + 1] += f.y; }
+        }
     }
     __nv_bfloat162 o[4];
 #pragma unroll

@@ -42,6 +42,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--layer", default="", help="cin,cout,level_delta[,ksize]: time ONE APRConv layer (forward + backward) instead of the U-Net")
+    ap.add_argument("--batch-inference", type=int, default=0,
+                    help="configs[3] of BASELINE.json: forward-only U-Net over this many independent APRs (256^3 images, 50-400 blobs), "
+                         "split over the ranks with no collective; reports aggregate particles/s")
     ap.add_argument("--profile-step", action="store_true",
                     help="after the timed region run one more step between cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     return ap.parse_args()
@@ -386,6 +389,80 @@ def run_gpu(args):
 
 
 # ---------------------------------------------------------------------------------------------
+# batch inference over independent APRs (configs[3] of BASELINE.json): no data-path collective
+# ---------------------------------------------------------------------------------------------
+def run_batch_inference(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    import pyapr
+    from pyapr.aprnet import cuda as ops
+    from _pyaprwrapper.aprnet import cuda as C
+    from apr_unet import APRUNet
+    from pyapr.sharding import shard_indices
+    C.set_conv_precision("bf16" if args.dtype == "bf16" else "fp32")
+    torch.manual_seed(7)
+    model = APRUNet(ops, 1, 2, depth=args.depth, n_filters_base=args.base).to(dev).eval()
+    rng = np.random.RandomState(4000)
+    blob_counts = rng.randint(50, 401, size=args.batch_inference)
+    mine = shard_indices(args.batch_inference, rank, world)
+    items = []
+    for i in mine:                                   # image i -> rank i mod world; nothing is exchanged
+        arrays, feat, _ = make_inputs((256, 256, 256), int(blob_counts[i]), 4000 + int(i), dev)
+        apr = pyapr.apr_from_arrays(arrays, "img%d" % i)
+        apr.init_cuda()
+        for dl in range(args.depth + 1):
+            apr.plan(dl)
+        items.append((apr, torch.from_numpy(feat)[None, None].contiguous().to(dev), arrays.n_particles))
+    n_local = sum(it[2] for it in items)
+
+    def sweep():
+        with torch.no_grad():
+            for apr, x, _ in items:
+                model(x, [apr])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(1, args.warmup)):
+        sweep()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        sweep()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1), float(n_local)], dtype=torch.float64, device=dev)
+    if world > 1:
+        tmax, tsum = t.clone(), t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        ms, n_total = float(tmax[0]), float(tsum[1])
+        dist.destroy_process_group()
+    else:
+        ms, n_total = float(t[0]), float(t[1])
+    if rank != 0:
+        return None
+    ms_per_sweep = ms / args.steps
+    return {"metric": "APR U-Net forward particles/s (batch inference)", "value": n_total / (ms_per_sweep * 1e-3), "unit": "particles/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(1, args.warmup), "ms_per_step": ms_per_sweep, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
+            "config": {"workload": "forward-only 4-level APR U-Net (base %d) over %d independent APRs from seeded 256x256x256 blob volumes "
+                                   "(50-400 blobs each), image i on rank i mod %d, no collective" % (args.base, args.batch_inference, world),
+                       "particles_total": int(n_total)}}
+
+
+# ---------------------------------------------------------------------------------------------
 # single-layer mode (APRConv channel sweep: configs[4] of BASELINE.json)
 # ---------------------------------------------------------------------------------------------
 def run_layer(args):
@@ -477,7 +554,7 @@ def main():
                "e2e": {"value": cb["value"], "unit": "particles/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         emit(out)
         return
-    out = run_layer(args) if args.layer else run_gpu(args)
+    out = run_layer(args) if args.layer else (run_batch_inference(args) if args.batch_inference else run_gpu(args))
     if out is not None:
         emit(out)
 
