@@ -368,11 +368,17 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
                         const int n = ti.ntile * NT + c0 + jj;
                         if (n < P.n_dim) P.out[(ll) n * P.ld_out + p] = __uint_as_float(r[jj]);
                     }
-                } else if (valid) {          // this thread is the only writer of its target
+                } else if (valid) {          // this thread is the only writer of its target: read all, then add and write
+                    float old[32];
 #pragma unroll
                     for (int jj = 0; jj < 32; ++jj) {
                         const int n = ti.ntile * NT + c0 + jj;
-                        if (n < P.n_dim) acc_dst[(ll) n * acc_ld] += __uint_as_float(r[jj]);
+                        old[jj] = n < P.n_dim ? acc_dst[(ll) n * acc_ld] : 0.f;
+                    }
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj) {
+                        const int n = ti.ntile * NT + c0 + jj;
+                        if (n < P.n_dim) acc_dst[(ll) n * acc_ld] = old[jj] + __uint_as_float(r[jj]);
                     }
                 }
             }
