@@ -1,7 +1,8 @@
-from .maxpool import MaxPool
+"""CUDA modules of the particle-domain CNN operators (names as in the reference package)."""
 from .conv import APRConv
-from .upsample import UpSampleConst
+from .maxpool import MaxPool
 from .norm import GroupNormReLU
+from .upsample import UpSampleConst
 from .utils import Reconstruct, SampleParticles
 
-__all__ = ["MaxPool", "APRConv", "UpSampleConst", "GroupNormReLU", "Reconstruct", "SampleParticles"]
+__all__ = ["APRConv", "MaxPool", "UpSampleConst", "GroupNormReLU", "Reconstruct", "SampleParticles"]

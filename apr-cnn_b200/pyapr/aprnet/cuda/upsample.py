@@ -1,34 +1,36 @@
-"""`UpSampleConst`: restore the next finer level by nearest-parent copy
-(reference: pyapr/aprnet/cuda/upsample.py:8-38)."""
+"""`UpSampleConst`: the inverse move of `MaxPool` — features of level delta d are carried to d - 1, every
+particle and node of the restored level taking the value of its parent node
+(reference module: pyapr/aprnet/cuda/upsample.py:8-38)."""
 from torch import nn
 from torch.autograd import Function
 
+from _pyaprwrapper import aprnet as _ext
 from _pyaprwrapper.data_containers import APRPtrVector
-from _pyaprwrapper.aprnet.cuda import upsample_const_backward, upsample_const_forward
 
 
-class UpsampleConstFunction(Function):
-    @staticmethod
-    def forward(ctx, inputs, aprs, level_deltas, decrement_level_deltas):
-        ctx.aprs = aprs
-        ctx.save_for_backward(level_deltas.clone())
-        output = upsample_const_forward(APRPtrVector(aprs), inputs, level_deltas)
-        if decrement_level_deltas:
-            level_deltas.sub_(1)
-        return output
+class _NearestParent(Function):
+    """Forward copies parent values down; backward sums the children's gradients into the parent."""
 
     @staticmethod
-    def backward(ctx, grad_output):
-        level_deltas, = ctx.saved_tensors
-        grad_input = upsample_const_backward(APRPtrVector(ctx.aprs), grad_output.contiguous(), level_deltas)
-        return grad_input, None, None, None
+    def forward(ctx, coarse, apr_list, deltas, step_deltas):
+        ctx.apr_list = apr_list
+        ctx.deltas_at_call = deltas.clone()               # the shared tensor is changed below
+        fine = _ext.cuda.upsample_const_forward(APRPtrVector(apr_list), coarse, deltas)
+        if step_deltas:
+            deltas.sub_(1)                                # callers thread one level_deltas tensor through the network
+        return fine
+
+    @staticmethod
+    def backward(ctx, grad_fine):
+        grad_coarse = _ext.cuda.upsample_const_backward(APRPtrVector(ctx.apr_list), grad_fine.contiguous(), ctx.deltas_at_call)
+        return grad_coarse, None, None, None
 
 
 class UpSampleConst(nn.Module):
     def __init__(self):
         super().__init__()
-        # When True the shared level_deltas tensor is decremented after the call (see MaxPool).
+        # the shared level_deltas tensor is decremented after the call unless this is cleared (see MaxPool)
         self.decrement_level_deltas = True
 
     def forward(self, input_features, aprs, level_deltas):
-        return UpsampleConstFunction.apply(input_features, aprs, level_deltas, self.decrement_level_deltas)
+        return _NearestParent.apply(input_features, aprs, level_deltas, self.decrement_level_deltas)
