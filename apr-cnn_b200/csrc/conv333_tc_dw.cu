@@ -99,35 +99,47 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
     tc_fence_after();
     const uint32_t tmem_d = *tmem_slot;
     bool failed = false;
+#ifdef APRNET_TC_DBG_TIMING
+    long long wt[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long w0 = clock64(); const long long wstart = w0;
+#define WT(i) { const long long w1 = clock64(); wt[i] += w1 - w0; w0 = w1; }
+#else
+#define WT(i)
+#endif
 
     if (warp < 8 && total_stages > 0) {
         // ---------------- producers ----------------
         const int gq = warp >> 2, wq = warp & 3;        // stage parity handled / 32-particle quarter of the stage
         const int c = lane % PC, r0 = lane / PC;
         constexpr int RPI = 32 / PC;                    // particles covered by one copy instruction
-        int32_t rows_cur[TPT], rows_nxt[TPT];
-        auto load_rows = [&](int s, int32_t (&rows)[TPT]) {      // source rows of this lane's particle for the taps of stage s
+        int32_t rows_cur[TPT], raw_nxt[TPT];
+        // table entries of this lane's particle for the taps of stage s: requested here, decoded only when the
+        // stage is issued, so that the load latency overlaps the copies of the stage in between
+        auto request_rows = [&](int s, int32_t (&raw)[TPT]) {
             const int chunk = s / MT, mt = s - chunk * MT;
             const ll p = pb + (ll) chunk * PT + wq * 32 + lane;
 #pragma unroll
             for (int tl = 0; tl < TPT; ++tl) {
                 const int t = mt * TPT + tl;
-                ll r = P.zero_row;
-                if (p < pe && t < ntaps) {
-                    const int32_t v = __ldg(P.nbr + (ll) (tap0 + t) * P.N + p);
-                    if (v >= 0) r = v; else if (v != APRNET_NONE) r = P.tree_base + aprnet_dec_tree(v);
-                }
-                rows[tl] = (int32_t) r;
+                raw[tl] = (p < pe && t < ntaps) ? __ldg(P.nbr + (ll) (tap0 + t) * P.N + p) : APRNET_NONE;
+            }
+        };
+        auto decode_rows = [&](const int32_t (&raw)[TPT], int32_t (&rows)[TPT]) {
+#pragma unroll
+            for (int tl = 0; tl < TPT; ++tl) {
+                const int32_t v = raw[tl];
+                rows[tl] = (int32_t) (v >= 0 ? (ll) v : (v == APRNET_NONE ? P.zero_row : P.tree_base + aprnet_dec_tree(v)));
             }
         };
         int s = gq;
-        if (s < total_stages) load_rows(s, rows_cur);
+        if (s < total_stages) { request_rows(s, raw_nxt); decode_rows(raw_nxt, rows_cur); }
         while (s < total_stages) {
             const int s_nxt = s + 2;
-            if (s_nxt < total_stages) load_rows(s_nxt, rows_nxt);      // in flight while this stage is issued
+            if (s_nxt < total_stages) request_rows(s_nxt, raw_nxt);      // in flight while this stage is issued
             const int chunk = s / MT, mt = s - chunk * MT;
             const uint32_t slot = (uint32_t) s % (uint32_t) nstage, use = (uint32_t) s / (uint32_t) nstage;
+            WT(0);
             if (use > 0 && !mbar_wait_warp(smem_u32(empty + slot), (use - 1) & 1, abort_flag)) { failed = true; break; }
+            WT(1);
             if (mt == 0) {
                 // this warp's 32 rows of the dO chunk
                 const uint32_t db = chunk & 1, duse = chunk >> 1;
@@ -142,6 +154,7 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
                 }
                 cp_async_arrive_noinc(smem_u32(dfull + db));
             }
+            WT(2);
             unsigned char* a_s = a_ring + (size_t) slot * A_STAGE;
             const __nv_bfloat16* src0 = P.xrows + cib * CIB + c * 8;
 #pragma unroll
@@ -158,9 +171,10 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
                 }
             }
             // the stage's barrier receives this thread's arrival when the copies above have landed
+            WT(3);
             cp_async_arrive_noinc(smem_u32(full + slot));
-#pragma unroll
-            for (int tl = 0; tl < TPT; ++tl) rows_cur[tl] = rows_nxt[tl];
+            if (s_nxt < total_stages) decode_rows(raw_nxt, rows_cur);
+            WT(4);
             s = s_nxt;
         }
         cp_async_commit();
@@ -173,8 +187,11 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
                 const uint32_t db = chunk & 1, duse = chunk >> 1;
                 const uint32_t b_addr = smem_u32(g_ring + db * G_BYTES);
                 for (int mt = 0; mt < MT; ++mt) {
+                    WT(0);
                     if (!mbar_wait(smem_u32(full + slot), use & 1, abort_flag)) { failed = true; break; }
+                    WT(1);
                     if (mt == 0 && !mbar_wait(smem_u32(dfull + db), duse & 1, abort_flag)) { failed = true; break; }
+                    WT(2);
                     fence_proxy_async();          // generic-proxy writes of the cp.async copies -> tensor-core (async proxy) reads
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(a_ring + (size_t) slot * A_STAGE);
@@ -185,8 +202,10 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
                         const uint64_t dbd = make_desc(b_addr + k * 2048, ATOM_STRIDE, 1024, 2);
                         umma_bf16(tmem_d + mt * NCOL, da, dbd, IDESC, (chunk > 0 || k > 0) ? 1u : 0u);
                     }
+                    WT(3);
                     umma_commit(smem_u32(empty + slot));
                     if (mt == MT - 1) umma_commit(smem_u32(dempty + db));
+                    WT(4);
                     if (++slot == (uint32_t) nstage) { slot = 0; ++use; }
                 }
             }
@@ -194,6 +213,11 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
         }
     }
 
+#ifdef APRNET_TC_DBG_TIMING
+    if (blockIdx.x == 7 && blockIdx.y == 0 && (tid == 0 || tid == 128 || tid == 256)) {
+        printf("dw tid %d total %lld | %lld %lld %lld %lld %lld | stages %d MT %d chunks %d\n", tid, clock64() - wstart, wt[0], wt[1], wt[2], wt[3], wt[4], nstage, MT, nchunks);
+    }
+#endif
     // ---------------- epilogue: warps 0-3 ----------------
     float* dst = P.partial + (ll) blockIdx.x * P.cout * P.cin * 27;
     if (warp < 4 && total_stages > 0 && !failed) {
