@@ -139,7 +139,7 @@ struct TcParams {
 };
 
 // ---- warp-specialised gather kernel ---------------------------------------------------------------
-// One persistent block per SM, 14 warps (forward pass and same-level input gradient):
+// One persistent block per SM, 13 warps (forward pass and both parts of the input gradient):
 //   warps 0-7   producers.  A stage (one tap, KS channels, 128 rows) belongs to ONE warp: warp w fills the
 //               stages w, w + 8, w + 16 ... of the block's stage sequence, so eight stages are being issued
 //               at once and the per-stage bookkeeping (slot wait, weight copy, barrier arrival) is paid
@@ -150,12 +150,12 @@ struct TcParams {
 //   warp 8      one thread issues the tcgen05.mma of each stage, in stage order, as soon as its barrier
 //               completes, and commits the stage's "slot free" barrier; accumulators rotate through
 //               NACC TMEM buffers so that later tiles start while earlier ones are read back;
-//   warps 10-13 epilogue: TMEM -> registers -> global for tile i; the neighbour-table entries of tile
+//   warps 9-12  epilogue: TMEM -> registers -> global for tile i; the neighbour-table entries of tile
 //               i + NIDX are requested into registers before the wait for tile i and decoded into the
 //               source-row buffer tile i has released afterwards, so their DRAM latency is never exposed.
 // All waits are bounded and poll a block-wide abort flag.
 constexpr int WS_NPROD = 8;
-constexpr int WS_THREADS = (WS_NPROD + 6) * 32;
+constexpr int WS_THREADS = (WS_NPROD + 5) * 32;
 constexpr int WS_MAX_STAGES = 20;
 constexpr int WS_MAX_ACC = 4;
 constexpr int WS_NIDX = 3;
@@ -312,7 +312,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
                 if (!failed) umma_commit(smem_u32(tmem_full + acc));
             }
         }
-    } else if (warp >= WS_NPROD + 2) {
+    } else if (warp >= WS_NPROD + 1) {
         // ---------------- epilogue + source-row staging ----------------
         const int q = warp & 3;                           // TMEM lane group this warp may read
         const int row = q * 32 + lane;
@@ -369,16 +369,19 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
                         if (n < P.n_dim) P.out[(ll) n * P.ld_out + p] = __uint_as_float(r[jj]);
                     }
                 } else if (valid) {          // this thread is the only writer of its target: read all, then add and write
-                    float old[32];
 #pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) {
-                        const int n = ti.ntile * NT + c0 + jj;
-                        old[jj] = n < P.n_dim ? acc_dst[(ll) n * acc_ld] : 0.f;
-                    }
+                    for (int h = 0; h < 32; h += 16) {        // 16 independent loads at a time
+                        float old[16];
 #pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) {
-                        const int n = ti.ntile * NT + c0 + jj;
-                        if (n < P.n_dim) acc_dst[(ll) n * acc_ld] = old[jj] + __uint_as_float(r[jj]);
+                        for (int jj = 0; jj < 16; ++jj) {
+                            const int n = ti.ntile * NT + c0 + h + jj;
+                            old[jj] = n < P.n_dim ? acc_dst[(ll) n * acc_ld] : 0.f;
+                        }
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) {
+                            const int n = ti.ntile * NT + c0 + h + jj;
+                            if (n < P.n_dim) acc_dst[(ll) n * acc_ld] = old[jj] + __uint_as_float(r[h + jj]);
+                        }
                     }
                 }
             }
@@ -393,7 +396,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
     }
 
 #ifdef APRNET_TC_DBG_TIMING
-    if (blockIdx.x == 7 && (tid == 0 || tid == 32 * WS_NPROD || tid == 32 * (WS_NPROD + 2))) {
+    if (blockIdx.x == 7 && (tid == 0 || tid == 32 * WS_NPROD || tid == 32 * (WS_NPROD + 1))) {
         const long long tot = clock64() - wstart;
         printf("ws tid %d total %lld | %lld %lld %lld %lld %lld %lld %lld %lld | stages %d nacc %d tiles %d steps/tile %d\n", tid, tot, wt[0], wt[1], wt[2], wt[3], wt[4], wt[5], wt[6], wt[7], stages, NACC, my_tiles, steps_per_tile);
     }
