@@ -24,6 +24,7 @@
 #include "apr_device.cuh"
 #include "tc_ptx.cuh"
 #include <cuda_bf16.h>
+#include <cuda.h>
 #include <algorithm>
 #include <cstring>
 #include <cstdlib>
@@ -136,6 +137,7 @@ struct TcParams {
     // added to out[:, t] for t < out_split and to out2[:, t - out_split] otherwise
     const int32_t* out_map; ll out_split;
     float* out2; ll ld_out2;
+    int use_tma;                           // source rows are fetched by the TMA unit (tile::gather4) instead of cp.async
 };
 
 // ---- warp-specialised gather kernel ---------------------------------------------------------------
@@ -146,7 +148,10 @@ struct TcParams {
 //               once per 4 * KS / 8 copy instructions.  Lane 0 streams the stage's weight tile with one bulk
 //               copy (byte-counting arrival); every lane attaches an asynchronous arrival to the stage's
 //               barrier (cp.async.mbarrier.arrive.noinc), so the stage is handed to the MMA warp the moment
-//               its copies land.  Producers only block on a ring slot the tensor core still reads;
+//               its copies land.  Producers only block on a ring slot the tensor core still reads.
+//               With use_tma the 128 row pieces of a stage are 32 tile::gather4 copies (one per lane, four
+//               rows each) through a tensor map of the packed rows whose swizzle mode equals the operand's:
+//               the TMA unit writes the swizzled layout itself and the copies bypass the L1 data pipe;
 //   warp 8      one thread issues the tcgen05.mma of each stage, in stage order, as soon as its barrier
 //               completes, and commits the stage's "slot free" barrier; accumulators rotate through
 //               NACC TMEM buffers so that later tiles start while earlier ones are read back;
@@ -175,7 +180,7 @@ __device__ __forceinline__ TileInfo tile_info(const TcParams& P, int work) {
 }
 
 template<int NT, int KS, int NACC>
-__global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcParams P, const int stages) {
+__global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcParams P, const int stages, const __grid_constant__ CUtensorMap row_map) {
     // A operand: K-major with the hardware swizzle whose width equals the row piece of one stage (KS
     // channels = 32, 64 or 128 bytes).  A gathered row piece is then contiguous in shared memory as it is
     // in global memory (its 16-byte chunks permuted inside the piece), so the lanes that copy one piece
@@ -213,7 +218,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
     const int nprod = min(WS_NPROD, stages);
 
     if (tid == 0) {
-        for (int i = 0; i < stages; ++i) { mbar_init(smem_u32(full + i), 32 + 1); mbar_init(smem_u32(empty + i), 1); }
+        for (int i = 0; i < stages; ++i) { mbar_init(smem_u32(full + i), P.use_tma ? 1 : 32 + 1); mbar_init(smem_u32(empty + i), 1); }
         for (int i = 0; i < NACC; ++i) { mbar_init(smem_u32(tmem_full + i), 1); mbar_init(smem_u32(tmem_empty + i), 4); }
         for (int i = 0; i < NIDX; ++i) mbar_init(smem_u32(idx_full + i), 4);
         *abort_flag = 0;
@@ -261,9 +266,19 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
                 WT(1);
                 unsigned char* a_s = stage_base + (size_t) slot * STAGE_BYTES;
                 if (lane == 0) {
-                    mbar_expect_tx(smem_u32(full + slot), B_BYTES);
+                    mbar_expect_tx(smem_u32(full + slot), P.use_tma ? A_BYTES + B_BYTES : B_BYTES);
                     bulk_copy_g2s(smem_u32(a_s + A_BYTES), wsrc + (ll) tap * w_tap_stride + (ll) kc * KS * NT * 2, B_BYTES, smem_u32(full + slot));
                     bulk_issued = true;
+                }
+                if (P.use_tma) {
+                    // lane l fetches rows 4l..4l+3; the bytes count against the arrival announced above (an
+                    // early completion only drives the byte count negative until lane 0's announcement)
+                    const int4 r = *reinterpret_cast<const int4*>(idx + tap * TILE_M + 4 * lane);
+                    tma_gather4(smem_u32(a_s + 4 * lane * ROW_BYTES), &row_map, kc * KS, r.x, r.y, r.z, r.w, smem_u32(full + slot));
+                    bulk_issued = true;
+                    g += nprod; step += nprod; slot += nprod;
+                    if (slot >= (uint32_t) stages) { slot -= stages; ++use; }
+                    continue;
                 }
                 const int32_t* idx_t = idx + tap * TILE_M + r0;
                 const __nv_bfloat16* src0 = P.rows + kc * KS + j * 8;
@@ -294,7 +309,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
                 for (int step = 0; step < steps_per_tile; ++step) {
                     if (!mbar_wait(smem_u32(full + slot), use & 1, abort_flag)) { failed = true; break; }
                     WT(1);
-                    fence_proxy_async();          // generic-proxy writes of the cp.async copies -> tensor-core (async proxy) reads
+                    if (!P.use_tma) fence_proxy_async();          // generic-proxy writes of the cp.async copies -> tensor-core (async proxy) reads
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(stage_base + (size_t) slot * STAGE_BYTES);
                     const uint32_t b_addr = a_addr + A_BYTES;
@@ -441,8 +456,42 @@ TcGeom tc_geometry(ll rows, int k_dim, int n_dim, int slots) {
     return g;
 }
 
+// Tensor map of the packed rows [n_rows][kpad] (bf16) with a box of one row piece (ks channels) and the
+// swizzle mode whose span equals the piece: tile::gather4 copies four such pieces per instruction.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int make_row_map(CUtensorMap* map, const void* rows, ll n_rows, int kpad, int ks) {
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+            cudaGetLastError();
+            return APRNET_ERR_UNSUPPORTED;
+        }
+        encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    if ((reinterpret_cast<uintptr_t>(rows) & 15) || n_rows <= 0 || n_rows >= (1ll << 31)) return APRNET_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t) kpad, (cuuint64_t) n_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t) kpad * 2};
+    const cuuint32_t box[2] = {(cuuint32_t) ks, 1};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapSwizzle sw = ks == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : (ks == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(rows), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? APRNET_OK : APRNET_ERR_UNSUPPORTED;
+}
+
+inline int tma_gather_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("APRNET_TC_GATHER"); v = (e && !strcmp(e, "tma")) ? 1 : 0; }
+    return v;
+}
+
 template<int NT, int KS>
-int launch_tc_ws(const TcParams& P, int total_tiles, cudaStream_t st, const char* pname) {
+int launch_tc_ws(TcParams P, int total_tiles, cudaStream_t st, const char* pname) {
     constexpr size_t STAGE = (size_t) TILE_M * KS * 2 + (size_t) NT * KS * 2;
     constexpr size_t FIXED = (size_t) WS_NIDX * 27 * TILE_M * 4 + (2 * WS_MAX_STAGES + 3 * WS_MAX_ACC) * 8 + 16 + 1024;      // + alignment slack
     constexpr int NACC = NT <= 128 ? 4 : 2;          // accumulators in flight: the SM's 512 TMEM columns, at most 4
@@ -457,8 +506,13 @@ int launch_tc_ws(const TcParams& P, int total_tiles, cudaStream_t st, const char
     const size_t smem = (size_t) stages * STAGE + FIXED;
     APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     const int grid = std::min(total_tiles, sms);
+    CUtensorMap row_map;
+    memset(&row_map, 0, sizeof(row_map));
+    // the map ends before the zero row: coordinate zero_row is then out of bounds and the TMA unit fills
+    // the piece with zeros without touching memory (one hot row would serialise on its L2 slice)
+    if (P.use_tma && make_row_map(&row_map, P.rows, P.zero_row, P.kpad, KS) != APRNET_OK) P.use_tma = 0;
     { AprnetProfScope _prof(pname, st);
-    kern<<<grid, WS_THREADS, smem, st>>>(P, stages);
+    kern<<<grid, WS_THREADS, smem, st>>>(P, stages, row_map);
     }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
@@ -515,6 +569,7 @@ int aprnet_tc_gather_conv(aprnet_apr* a, int dl, int backward, int cin, int cout
     P.wp = wp; P.out = out; P.ld_out = ld_out; P.n_dim = n_dim; P.n_tiles = g.n_tiles; P.same_level_only = backward;
     P.error_flag = g_error_flag_dev;
     P.out_map = nullptr; P.out_split = 0; P.out2 = nullptr; P.ld_out2 = 0;
+    P.use_tma = tma_gather_enabled();
 
     const int total = P.segs.tile_begin[P.segs.n] * g.n_tiles;
     if (total == 0) return APRNET_OK;

@@ -30,6 +30,12 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+// four rows of a 2-D tensor (row coordinates r0..r3, first column c) -> four consecutive row pieces of the
+// box width in shared memory, swizzled as the tensor map says; completion as transferred bytes
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tmap, int c, int r0, int r1, int r2, int r3, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];\n"
+                 ::"r"(dst), "l"(tmap), "r"(c), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar) : "memory");
+}
 
 // ---- mbarriers -----------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

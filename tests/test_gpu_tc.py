@@ -65,3 +65,21 @@ def test_conv333_tensor_core_path(name, cin, cout, nst, oracle, bf16_mode):
             assert H.rel_err(H.t2n(out[0]), want) <= tol_out, (name, dl, exact_inputs)
             assert H.rel_err(H.t2n(gi[0]), gi_ref) <= tol_gi, (name, dl, exact_inputs)
             assert H.rel_err(H.t2n(gw), gw_ref) <= tol_out, (name, dl, exact_inputs)
+
+
+def test_conv333_tma_gather_variant():
+    """The opt-in TMA (tile::gather4) source-row path gives the same parity as the default cp.async path.
+
+    The switch is read once per process, so the parity cases of this file run again in a child process.
+    """
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("APRNET_TC_GATHER") == "tma":
+        pytest.skip("already running with the TMA gather path")
+    env = dict(os.environ, APRNET_TC_GATHER="tma")
+    here = os.path.dirname(os.path.abspath(__file__))
+    res = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_gpu_tc.py"), "-m", "gpu", "-x", "-q",
+                          "-k", "tensor_core_path and (blob or odd)"], env=env, cwd=os.path.dirname(here),
+                         capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
