@@ -137,7 +137,7 @@ def unet_conv_layers(base, depth):
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture per kernel family on the 64->64
 # layer at level_delta 1 of a 256x512x512 volume, 1.77 M locations) divided by the algorithmic bytes of the
 # same operator call.  Every operand of these kernels is streamed, so traffic scales with the locations.
-NCU_TRAFFIC_RATIO = {"conv333_tc_dw": 2.82, "conv333_tc_fwd": 1.29, "conv333_tc_bwd_gather": 1.01}
+NCU_TRAFFIC_RATIO = {"conv333_tc_dw": 2.72, "conv333_tc_fwd": 1.36, "conv333_tc_bwd_gather": 1.29}
 
 
 def roofline_from_profile(prof, steps, nparts, ntree, peaks, layers, bf16):
