@@ -782,6 +782,9 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
     }, "mode"_a, "'fp32': exact CUDA-core kernels (default); 'bf16': tensor-core path for float32 3x3x3 convolutions (bf16 operands, fp32 accumulation)");
     cuda.def("get_conv_precision", []() { return std::string(g_conv_mode == 1 ? "bf16" : "fp32"); });
     cuda.def("tc_error_flag", []() { return aprnet_tc_error_flag(); });
+    cuda.def("tc_error_reset", []() { aprnet_tc_error_reset(); }, "Clear the flag that a tensor-core kernel raises when one of its bounded waits runs out");
+    cuda.def("tc_set_option", [](const std::string& name, int value) { check(aprnet_tc_set_option(name.c_str(), value), "tc_set_option"); },
+             "name"_a, "value"_a, "Switches of the tensor-core kernels ('tma_gather': 1 = source rows by TMA tile::gather4 instead of cp.async)");
     cuda.def("profile_enable", [](bool on) { aprnet_profile_enable(on ? 1 : 0); }, "on"_a,
              "Bracket every kernel launch of the library with CUDA events (benchmark use)");
     cuda.def("profile_read", []() {

@@ -27,7 +27,6 @@
 #include <cuda.h>
 #include <algorithm>
 #include <cstring>
-#include <cstdlib>
 
 namespace {
 
@@ -231,12 +230,6 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
     const uint32_t tmem_d = *tmem_slot;
     bool failed = false;
     bool bulk_issued = false;
-#ifdef APRNET_TC_DBG_TIMING
-    long long wt[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long w0 = clock64(); const long long wstart = w0;
-#define WT(i) { const long long w1 = clock64(); wt[i] += w1 - w0; w0 = w1; }
-#else
-#define WT(i)
-#endif
 
     if (warp < WS_NPROD) {
         // ---------------- producers ----------------
@@ -252,9 +245,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
                 while (step >= steps_per_tile) { step -= steps_per_tile; ++it; }
                 if (it != cur_it) {
                     cur_it = it;
-                    WT(7);
                     if (!mbar_wait_warp(smem_u32(idx_full + it % NIDX), (it / NIDX) & 1, abort_flag)) { failed = true; break; }
-                    WT(0);
                     idx = idx_s + (it % NIDX) * 27 * TILE_M;
                     if (lane == 0) {      // packed weights of one (slot, tap, n tile) are [k chunk][n][8]; a stage takes KS / 8 chunks
                         const TileInfo ti = tile_info(P, blockIdx.x + it * gridDim.x);
@@ -263,7 +254,6 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
                 }
                 const int tap = step / kchunks, kc = step - tap * kchunks;
                 if (use > 0 && !mbar_wait_warp(smem_u32(empty + slot), (use - 1) & 1, abort_flag)) { failed = true; break; }
-                WT(1);
                 unsigned char* a_s = stage_base + (size_t) slot * STAGE_BYTES;
                 if (lane == 0) {
                     mbar_expect_tx(smem_u32(full + slot), P.use_tma ? A_BYTES + B_BYTES : B_BYTES);
@@ -287,10 +277,8 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
                     const int row = i * RW + r0;
                     cp_async16(smem_u32(a_s + row * ROW_BYTES + (swizzled_chunk<KS>(row, j) << 4)), src0 + (ll) idx_t[i * RW] * P.kpad);
                 }
-                WT(2);
                 // the stage's barrier receives this thread's arrival when the copies above have landed
                 cp_async_arrive_noinc(smem_u32(full + slot));
-                WT(3);
                 g += nprod; step += nprod; slot += nprod;
                 if (slot >= (uint32_t) stages) { slot -= stages; ++use; }
             }
@@ -305,23 +293,19 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
                 const uint32_t acc = (uint32_t) it % NACC, acc_use = (uint32_t) it / NACC;
                 if (acc_use > 0 && !mbar_wait(smem_u32(tmem_empty + acc), (acc_use - 1) & 1, abort_flag)) { failed = true; break; }
                 tc_fence_after();
-                WT(0);
                 for (int step = 0; step < steps_per_tile; ++step) {
                     if (!mbar_wait(smem_u32(full + slot), use & 1, abort_flag)) { failed = true; break; }
-                    WT(1);
                     if (!P.use_tma) fence_proxy_async();          // generic-proxy writes of the cp.async copies -> tensor-core (async proxy) reads
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(stage_base + (size_t) slot * STAGE_BYTES);
                     const uint32_t b_addr = a_addr + A_BYTES;
+                    // descriptors of the stage's first MMA; the others add the encoded byte offset of their K slice
+                    const uint64_t da0 = make_desc(a_addr, 16, 8 * ROW_BYTES, A_LAYOUT);
+                    const uint64_t db0 = make_desc(b_addr, NT * 16, 128, 0);
 #pragma unroll
-                    for (int k = 0; k < KS / 16; ++k) {
-                        const uint64_t da = make_desc(a_addr + k * 32, 16, 8 * ROW_BYTES, A_LAYOUT);
-                        const uint64_t db = make_desc(b_addr + k * 2 * (NT * 16), NT * 16, 128, 0);
-                        umma_bf16(tmem_d + acc * NT, da, db, IDESC, (step > 0 || k > 0) ? 1u : 0u);
-                    }
-                    WT(2);
+                    for (int k = 0; k < KS / 16; ++k)
+                        umma_bf16(tmem_d + acc * NT, da0 + (uint64_t) (k * 2), db0 + (uint64_t) (k * 2 * NT), IDESC, (step > 0 || k > 0) ? 1u : 0u);
                     umma_commit(smem_u32(empty + slot));
-                    WT(3);
                     if (++slot == (uint32_t) stages) { slot = 0; ++use; }
                 }
                 if (!failed) umma_commit(smem_u32(tmem_full + acc));
@@ -356,7 +340,6 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
         };
         for (int it = 0; it < NIDX; ++it) { request_idx(it); publish_idx(it); }
         for (int it = 0; it < my_tiles; ++it) {
-            WT(7);
             const TileInfo ti = tile_info(P, blockIdx.x + it * gridDim.x);
             const ll p = ti.p0 + row;
             const bool valid = p < ti.hi;
@@ -368,9 +351,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
             }
             const uint32_t acc = (uint32_t) it % NACC, acc_use = (uint32_t) it / NACC;
             request_idx(it + NIDX);       // lands while this warp waits for the accumulator
-            WT(2);
             if (!mbar_wait_warp(smem_u32(tmem_full + acc), acc_use & 1, abort_flag)) { failed = true; break; }
-            WT(0);
             tc_fence_after();
 #pragma unroll
             for (int c0 = 0; c0 < NT; c0 += 32) {
@@ -403,19 +384,11 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(tmem_empty + acc));
-            WT(1);
             // every copy that read the source rows of tile `it` has landed (its accumulator is complete)
             publish_idx(it + NIDX);
-            WT(3);
         }
     }
 
-#ifdef APRNET_TC_DBG_TIMING
-    if (blockIdx.x == 7 && (tid == 0 || tid == 32 * WS_NPROD || tid == 32 * (WS_NPROD + 1))) {
-        const long long tot = clock64() - wstart;
-        printf("ws tid %d total %lld | %lld %lld %lld %lld %lld %lld %lld %lld | stages %d nacc %d tiles %d steps/tile %d\n", tid, tot, wt[0], wt[1], wt[2], wt[3], wt[4], wt[5], wt[6], wt[7], stages, NACC, my_tiles, steps_per_tile);
-    }
-#endif
     // teardown (also the error path): the gather copies were drained above; after a failure the bulk
     // copies still in flight get time to land before the block's shared memory is released
     if (failed) {
@@ -484,11 +457,9 @@ int make_row_map(CUtensorMap* map, const void* rows, ll n_rows, int kpad, int ks
     return r == CUDA_SUCCESS ? APRNET_OK : APRNET_ERR_UNSUPPORTED;
 }
 
-inline int tma_gather_enabled() {
-    static int v = -1;
-    if (v < 0) { const char* e = getenv("APRNET_TC_GATHER"); v = (e && !strcmp(e, "tma")) ? 1 : 0; }
-    return v;
-}
+int g_tma_gather = 0;      // aprnet_tc_set_option("tma_gather", 1): source rows by TMA tile::gather4 instead of cp.async
+
+inline int tma_gather_enabled() { return g_tma_gather; }
 
 template<int NT, int KS>
 int launch_tc_ws(TcParams P, int total_tiles, cudaStream_t st, const char* pname) {
@@ -501,7 +472,6 @@ int launch_tc_ws(TcParams P, int total_tiles, cudaStream_t st, const char* pname
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     // one block per SM with all of its shared memory (227 KB, 1 KB reserved) as the stage ring
     int stages = (int) std::min<size_t>(WS_MAX_STAGES, (227 * 1024 - 1024 - FIXED) / STAGE);
-    if (const char* e = getenv("APRNET_TC_WS_STAGES")) stages = std::max(2, std::min(stages, atoi(e)));
     if (stages < 2) { aprnet_set_error("conv333 tensor-core path: tile nt=%d ks=%d does not fit shared memory", NT, KS); return APRNET_ERR_UNSUPPORTED; }
     const size_t smem = (size_t) stages * STAGE + FIXED;
     APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
@@ -626,6 +596,15 @@ size_t aprnet_tc_weight_bytes(int k_dim, int n_dim, int slots) { return tc_geome
 int aprnet_tc_pad(int channels) { return pad_to(channels, 16); }
 
 extern "C" int aprnet_tc_error_flag(void) { return g_error_flag_host ? *g_error_flag_host : 0; }
+
+extern "C" void aprnet_tc_error_reset(void) { if (g_error_flag_host) *g_error_flag_host = 0; }
+
+extern "C" int aprnet_tc_set_option(const char* name, int value) {
+    APRNET_ARG_CHECK(name, "null option name");
+    if (!strcmp(name, "tma_gather")) { g_tma_gather = value != 0; return APRNET_OK; }
+    aprnet_set_error("aprnet_tc_set_option: unknown option '%s'", name);
+    return APRNET_ERR_ARG;
+}
 
 extern "C" int64_t aprnet_conv333_tc_workspace_bytes(const aprnet_apr* a, int dl, int cin, int cout, int slots) {
     if (!a || !a->valid_dl(dl)) return -1;

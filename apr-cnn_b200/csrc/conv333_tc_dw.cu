@@ -20,7 +20,6 @@
 #include "tc_ptx.cuh"
 #include <cuda_bf16.h>
 #include <algorithm>
-#include <cstdlib>
 
 namespace {
 
@@ -99,12 +98,6 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
     tc_fence_after();
     const uint32_t tmem_d = *tmem_slot;
     bool failed = false;
-#ifdef APRNET_TC_DBG_TIMING
-    long long wt[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long w0 = clock64(); const long long wstart = w0;
-#define WT(i) { const long long w1 = clock64(); wt[i] += w1 - w0; w0 = w1; }
-#else
-#define WT(i)
-#endif
 
     if (warp < 8 && total_stages > 0) {
         // ---------------- producers ----------------
@@ -137,9 +130,7 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
             if (s_nxt < total_stages) request_rows(s_nxt, raw_nxt);      // in flight while this stage is issued
             const int chunk = s / MT, mt = s - chunk * MT;
             const uint32_t slot = (uint32_t) s % (uint32_t) nstage, use = (uint32_t) s / (uint32_t) nstage;
-            WT(0);
             if (use > 0 && !mbar_wait_warp(smem_u32(empty + slot), (use - 1) & 1, abort_flag)) { failed = true; break; }
-            WT(1);
             if (mt == 0) {
                 // this warp's 32 rows of the dO chunk
                 const uint32_t db = chunk & 1, duse = chunk >> 1;
@@ -154,7 +145,6 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
                 }
                 cp_async_arrive_noinc(smem_u32(dfull + db));
             }
-            WT(2);
             unsigned char* a_s = a_ring + (size_t) slot * A_STAGE;
             const __nv_bfloat16* src0 = P.xrows + cib * CIB + c * 8;
 #pragma unroll
@@ -171,10 +161,8 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
                 }
             }
             // the stage's barrier receives this thread's arrival when the copies above have landed
-            WT(3);
             cp_async_arrive_noinc(smem_u32(full + slot));
             if (s_nxt < total_stages) decode_rows(raw_nxt, rows_cur);
-            WT(4);
             s = s_nxt;
         }
         cp_async_commit();
@@ -187,11 +175,8 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
                 const uint32_t db = chunk & 1, duse = chunk >> 1;
                 const uint32_t b_addr = smem_u32(g_ring + db * G_BYTES);
                 for (int mt = 0; mt < MT; ++mt) {
-                    WT(0);
                     if (!mbar_wait(smem_u32(full + slot), use & 1, abort_flag)) { failed = true; break; }
-                    WT(1);
                     if (mt == 0 && !mbar_wait(smem_u32(dfull + db), duse & 1, abort_flag)) { failed = true; break; }
-                    WT(2);
                     fence_proxy_async();          // generic-proxy writes of the cp.async copies -> tensor-core (async proxy) reads
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(a_ring + (size_t) slot * A_STAGE);
@@ -202,10 +187,8 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
                         const uint64_t dbd = make_desc(b_addr + k * 2048, ATOM_STRIDE, 1024, 2);
                         umma_bf16(tmem_d + mt * NCOL, da, dbd, IDESC, (chunk > 0 || k > 0) ? 1u : 0u);
                     }
-                    WT(3);
                     umma_commit(smem_u32(empty + slot));
                     if (mt == MT - 1) umma_commit(smem_u32(dempty + db));
-                    WT(4);
                     if (++slot == (uint32_t) nstage) { slot = 0; ++use; }
                 }
             }
@@ -213,11 +196,6 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
         }
     }
 
-#ifdef APRNET_TC_DBG_TIMING
-    if (blockIdx.x == 7 && blockIdx.y == 0 && (tid == 0 || tid == 128 || tid == 256)) {
-        printf("dw tid %d total %lld | %lld %lld %lld %lld %lld | stages %d MT %d chunks %d\n", tid, clock64() - wstart, wt[0], wt[1], wt[2], wt[3], wt[4], nstage, MT, nchunks);
-    }
-#endif
     // ---------------- epilogue: warps 0-3 ----------------
     float* dst = P.partial + (ll) blockIdx.x * P.cout * P.cin * 27;
     if (warp < 4 && total_stages > 0 && !failed) {
@@ -328,8 +306,7 @@ extern "C" int aprnet_conv333_backward_weights_tc(aprnet_apr* a, int dl, int cin
     ll total_len = 0;
     for (const Segment& sg : segs) total_len += sg.end - sg.begin;
     if (total_len == 0) return APRNET_OK;
-    int waves = 2;
-    if (const char* e = getenv("APRNET_DW_WAVES")) waves = std::max(1, atoi(e));
+    const int waves = 2;
     ll want = std::max<ll>(1, ((ll) waves * sms + blocks_y - 1) / blocks_y);
     want = std::min<ll>(want, (total_len + 4 * PT - 1) / (4 * PT));
     want = std::max<ll>(1, std::min<ll>(max_ranges - (ll) segs.size(), want));

@@ -180,6 +180,12 @@ int aprnet_conv333_backward_input_cross_level_tc(aprnet_apr* apr, int level_delt
                                                  float* grad_tree_scratch, int64_t ld_tree, void* packed_weight_ws,
                                                  void* edge_ws, int64_t edge_ws_bytes, void* stream);
 int aprnet_tc_error_flag(void);
+/* Clears the flag above so that the tensor-core entry points accept calls again after a wait ran out. */
+void aprnet_tc_error_reset(void);
+/* Switches of the tensor-core kernels.  "tma_gather": 1 makes the forward and same-level input-gradient
+ * kernels fetch their source rows with TMA tile::gather4 copies through a tensor map of the packed rows
+ * instead of 16-byte cp.async copies (same results; default 0). */
+int aprnet_tc_set_option(const char* name, int value);
 
 /* ---- 1x1x1 convolution -----------------------------------------------------------------------
  * pyapr/aprnet/cuda/src/conv_gpu.hpp:98-120 (apply_conv111 / _backward).  weights (S, Cout, Cin);
