@@ -374,6 +374,128 @@ std::vector<torch::Tensor> conv333_backward_with_tree(std::vector<APR*>& aprs, t
     return conv333_backward_impl(aprs, input, weights, grad_output, level_delta, tree, need_grad_input);
 }
 
+// ---- 3x3x3 convolution, split forms for one z-slab of an APR per GPU (pyapr/aprnet/cuda/sharded.py) ----------
+// forward with given tree means (B, Cin, T); returns {output, kept}: kept = packed bf16 rows (bf16 mode) or an empty tensor
+std::vector<torch::Tensor> conv333_forward_pretree(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor tree, torch::Tensor weights,
+                                                   torch::Tensor level_delta) {
+    CHECK_INPUT(input); CHECK_INPUT(weights); CHECK_INPUT(tree);
+    check_batch(aprs, input);
+    TORCH_CHECK(weights.dim() == 6 && weights.size(3) == 3 && weights.size(4) == 3 && weights.size(5) == 3, "weights must be (levels, Cout, Cin, 3, 3, 3)");
+    TORCH_CHECK(input.size(1) == weights.size(2), "input tensor shape does not match weights tensor");
+    TORCH_CHECK(tree.dim() == 3 && tree.size(0) == input.size(0) && tree.size(1) == input.size(1) && tree.scalar_type() == input.scalar_type(),
+                "tree must be (batch, Cin, tree nodes) of the input's dtype");
+    c10::cuda::CUDAGuard guard(input.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    const int64_t cin = input.size(1), cout = weights.size(1), n = input.size(2), ldt = tree.size(2);
+    const int dt = dtype_id(input);
+    const bool tc = g_conv_mode == 1 && dt == APRNET_F32;
+    int64_t rows_bytes = 256, w_bytes = 256;
+    for (size_t i = 0; i < aprs.size(); ++i) {
+        check_level_delta(*aprs[i], dl[i]);
+        aprnet_apr* h = aprs[i]->handle(input);
+        TORCH_CHECK(aprs[i]->number_parts(dl[i]) <= n && aprnet_tree_size(h, dl[i]) <= ldt, "input or tree has fewer entries than the APR at this level delta");
+        if (tc) {
+            const int64_t rb = aprnet_conv333_tc_packed_rows_bytes(h, dl[i], (int) cin);
+            rows_bytes = std::max(rows_bytes, rb);
+            w_bytes = std::max(w_bytes, aprnet_conv333_tc_forward_workspace_bytes(h, dl[i], (int) cin, (int) cout, (int) weights.size(0)) - rb);
+        }
+    }
+    auto output = torch::empty({input.size(0), cout, n}, input.options());
+    torch::Tensor ws = tc ? torch::empty({input.size(0), rows_bytes + w_bytes}, input.options().dtype(torch::kUInt8)) : torch::Tensor();
+    for (int64_t b = 0; b < input.size(0); ++b) {
+        if (tc)
+            check(aprnet_conv333_forward_tc_pretree(aprs[b]->handle(input), dl[b], (int) cin, (int) cout, (int) weights.size(0), (const float*) row(input, b), n,
+                                                    (const float*) weights.data_ptr(), (float*) row(output, b), n, (const float*) row(tree, b), ldt,
+                                                    row(ws, b), stream_of(input)), "conv333_forward_pretree (tensor cores)");
+        else
+            check(aprnet_conv333_forward_pretree(aprs[b]->handle(input), dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(input, b), n,
+                                                 weights.data_ptr(), row(output, b), n, row(tree, b), ldt, stream_of(input)), "conv333_forward_pretree");
+        zero_padding(output, b, aprs[b]->number_parts(dl[b]));
+    }
+    return {output, tc ? ws : torch::empty({0}, input.options().dtype(torch::kUInt8))};
+}
+
+// backward without the tree adjoint: returns {grad_input (direct contributions), grad_tree (B, Cin, T), grad_weights}.
+// bf16 mode: `kept` is the rows buffer of conv333_forward_pretree and `input` is not read; otherwise input and tree are used.
+std::vector<torch::Tensor> conv333_backward_pretree(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor tree, torch::Tensor kept, torch::Tensor weights,
+                                                    torch::Tensor grad_output, torch::Tensor level_delta, bool need_grad_input) {
+    CHECK_INPUT(weights); CHECK_INPUT(grad_output); CHECK_INPUT(tree);
+    check_batch(aprs, grad_output);
+    c10::cuda::CUDAGuard guard(grad_output.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    const int64_t cin = weights.size(2), cout = weights.size(1), n = grad_output.size(2), ldt = tree.size(2), B = grad_output.size(0);
+    const int dt = dtype_id(grad_output);
+    const bool tc = g_conv_mode == 1 && dt == APRNET_F32 && kept.numel() > 0;
+    TORCH_CHECK(grad_output.size(1) == cout && tree.dim() == 3 && tree.size(0) == B && tree.size(1) == cin, "shapes do not match");
+    if (!tc) { CHECK_INPUT(input); TORCH_CHECK(input.dim() == 3 && input.size(1) == cin && input.size(2) == n, "input shape does not match"); }
+    auto grad_tree = torch::zeros({B, cin, ldt}, grad_output.options());
+    auto grad_weights = torch::zeros_like(weights);
+    torch::Tensor grad_input;
+    void* st = stream_of(grad_output);
+    if (tc) {
+        int64_t bytes = 256;
+        for (size_t i = 0; i < aprs.size(); ++i) {
+            check_level_delta(*aprs[i], dl[i]);
+            aprnet_apr* h = aprs[i]->handle(grad_output);
+            TORCH_CHECK(kept.dim() == 2 && kept.size(0) == B && kept.size(1) >= aprnet_conv333_tc_packed_rows_bytes(h, dl[i], (int) cin), "rows buffer too small for this APR");
+            bytes = std::max<int64_t>(bytes, aprnet_conv333_tc_workspace_bytes(h, dl[i], (int) cin, (int) cout, (int) weights.size(0)));
+        }
+        if (need_grad_input) grad_input = torch::empty({B, cin, n}, grad_output.options());
+        auto ws = torch::empty({bytes}, grad_output.options().dtype(torch::kUInt8));
+        auto partial = torch::empty({aprnet_conv333_tc_dw_partial_elems((int) cin, (int) cout)}, grad_output.options());
+        for (int64_t b = 0; b < B; ++b) {
+            check(aprnet_conv333_backward_tc_rows_pretree(aprs[b]->handle(grad_output), dl[b], (int) cin, (int) cout, (int) weights.size(0), row(kept, b),
+                                                          (const float*) row(grad_output, b), n, (const float*) weights.data_ptr(),
+                                                          need_grad_input ? (float*) row(grad_input, b) : nullptr, n, (float*) grad_weights.data_ptr(),
+                                                          (float*) row(grad_tree, b), ldt, (float*) partial.data_ptr(), ws.data_ptr(), st),
+                  "conv333_backward_pretree (tensor cores)");
+            if (need_grad_input) zero_padding(grad_input, b, aprs[b]->number_parts(dl[b]));
+        }
+    } else {
+        auto partial = torch::empty({aprnet_conv333_partial_elems((int) cin, (int) cout)}, grad_output.options());
+        grad_input = torch::zeros({B, cin, n}, grad_output.options());
+        for (int64_t b = 0; b < B; ++b) {
+            check_level_delta(*aprs[b], dl[b]);
+            aprnet_apr* h = aprs[b]->handle(grad_output);
+            check(aprnet_conv333_backward_weights(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(input, b), n, row(tree, b), ldt,
+                                                  row(grad_output, b), n, grad_weights.data_ptr(), partial.data_ptr(), st), "conv333_backward_weights");
+            if (need_grad_input)
+                check(aprnet_conv333_backward_input_pretree(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(grad_output, b), n,
+                                                            weights.data_ptr(), row(grad_input, b), n, row(grad_tree, b), ldt, st), "conv333_backward_input_pretree");
+        }
+    }
+    return {grad_input, grad_tree, grad_weights};
+}
+
+// tree means of a batch (B, C, N) -> (B, C, T); and the adjoint applied in place to grad_input / grad_tree
+torch::Tensor fill_tree_mean_batch(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor level_delta) {
+    CHECK_INPUT(input);
+    check_batch(aprs, input);
+    c10::cuda::CUDAGuard guard(input.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    int64_t max_tree = 1;
+    for (size_t i = 0; i < aprs.size(); ++i) { check_level_delta(*aprs[i], dl[i]); max_tree = std::max<int64_t>(max_tree, aprnet_tree_size(aprs[i]->handle(input), dl[i])); }
+    auto tree = torch::zeros({input.size(0), input.size(1), max_tree}, input.options());
+    for (int64_t b = 0; b < input.size(0); ++b)
+        check(aprnet_fill_tree_mean_forward(aprs[b]->handle(input), dl[b], dtype_id(input), (int) input.size(1), row(input, b), input.size(2),
+                                            row(tree, b), max_tree, stream_of(input)), "fill_tree_mean");
+    return tree;
+}
+
+void fill_tree_mean_backward_inplace(std::vector<APR*>& aprs, torch::Tensor grad_input, torch::Tensor grad_tree, torch::Tensor level_delta) {
+    CHECK_INPUT(grad_input); CHECK_INPUT(grad_tree);
+    check_batch(aprs, grad_input);
+    TORCH_CHECK(grad_tree.dim() == 3 && grad_tree.size(0) == grad_input.size(0) && grad_tree.size(1) == grad_input.size(1), "grad_tree must be (batch, channels, tree nodes)");
+    c10::cuda::CUDAGuard guard(grad_input.device());
+    const auto dl = read_level_delta(level_delta, aprs.size());
+    for (int64_t b = 0; b < grad_input.size(0); ++b) {
+        check_level_delta(*aprs[b], dl[b]);
+        TORCH_CHECK(aprnet_tree_size(aprs[b]->handle(grad_input), dl[b]) <= grad_tree.size(2), "grad_tree has fewer nodes than the APR at this level delta");
+        check(aprnet_fill_tree_mean_backward(aprs[b]->handle(grad_input), dl[b], dtype_id(grad_input), (int) grad_input.size(1), row(grad_input, b), grad_input.size(2),
+                                             row(grad_tree, b), grad_tree.size(2), stream_of(grad_input)), "fill_tree_mean_backward");
+    }
+}
+
 // ---- 1x1x1 convolution ------------------------------------------------------------------------
 torch::Tensor conv111_forward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights, torch::Tensor level_delta) {
     CHECK_INPUT(input); CHECK_INPUT(weights);
@@ -639,6 +761,59 @@ std::vector<torch::Tensor> groupnorm_relu_backward(torch::Tensor x, torch::Tenso
     return {dx, dgamma, dbeta};
 }
 
+// split forms of GroupNorm + ReLU (sums on this device, statistics from the caller)
+torch::Tensor groupnorm_row_sums(torch::Tensor x) {
+    CHECK_INPUT(x);
+    TORCH_CHECK(x.dim() == 3, "expected (batch, channels, n)");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto sums = torch::empty({x.size(0) * x.size(1), 2}, x.options().dtype(torch::kFloat64));
+    auto ws = torch::empty({aprnet_groupnorm_workspace_bytes((int) x.size(0), (int) x.size(1), 1)}, x.options().dtype(torch::kUInt8));
+    check(aprnet_groupnorm_row_sums(dtype_id(x), (int) x.size(0), (int) x.size(1), x.size(2), x.data_ptr(), ws.data_ptr(), sums.data_ptr<double>(), stream_of(x)), "groupnorm_row_sums");
+    return sums;
+}
+
+torch::Tensor groupnorm_relu_apply(torch::Tensor x, c10::optional<torch::Tensor> gamma, c10::optional<torch::Tensor> beta, torch::Tensor mean, torch::Tensor rstd,
+                                   int64_t groups, bool relu) {
+    CHECK_INPUT(x); CHECK_INPUT(mean); CHECK_INPUT(rstd);
+    TORCH_CHECK(x.dim() == 3 && x.size(1) % groups == 0 && mean.numel() == x.size(0) * groups && rstd.numel() == mean.numel() &&
+                mean.scalar_type() == x.scalar_type() && rstd.scalar_type() == x.scalar_type(), "statistics do not match the input");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto y = torch::empty_like(x);
+    const void* g = gamma.has_value() && gamma->defined() ? gamma->contiguous().data_ptr() : nullptr;
+    const void* b = beta.has_value() && beta->defined() ? beta->contiguous().data_ptr() : nullptr;
+    check(aprnet_groupnorm_relu_apply(dtype_id(x), (int) x.size(0), (int) x.size(1), x.size(2), (int) groups, x.data_ptr(), g, b, mean.data_ptr(), rstd.data_ptr(),
+                                      y.data_ptr(), relu ? 1 : 0, stream_of(x)), "groupnorm_relu_apply");
+    return y;
+}
+
+torch::Tensor groupnorm_backward_row_sums(torch::Tensor x, torch::Tensor grad_y, c10::optional<torch::Tensor> gamma, c10::optional<torch::Tensor> beta,
+                                          torch::Tensor mean, torch::Tensor rstd, int64_t groups, bool relu) {
+    CHECK_INPUT(x); CHECK_INPUT(grad_y); CHECK_INPUT(mean); CHECK_INPUT(rstd);
+    TORCH_CHECK(x.sizes() == grad_y.sizes() && x.dim() == 3 && x.size(1) % groups == 0, "grad_y must have the shape of x");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto sums = torch::empty({x.size(0) * x.size(1), 2}, x.options().dtype(torch::kFloat64));
+    auto ws = torch::empty({aprnet_groupnorm_workspace_bytes((int) x.size(0), (int) x.size(1), (int) groups)}, x.options().dtype(torch::kUInt8));
+    const void* g = gamma.has_value() && gamma->defined() ? gamma->contiguous().data_ptr() : nullptr;
+    const void* b = beta.has_value() && beta->defined() ? beta->contiguous().data_ptr() : nullptr;
+    check(aprnet_groupnorm_backward_row_sums(dtype_id(x), (int) x.size(0), (int) x.size(1), x.size(2), (int) groups, x.data_ptr(), grad_y.data_ptr(), g, b,
+                                             mean.data_ptr(), rstd.data_ptr(), ws.data_ptr(), sums.data_ptr<double>(), relu ? 1 : 0, stream_of(x)), "groupnorm_backward_row_sums");
+    return sums;
+}
+
+torch::Tensor groupnorm_backward_apply(torch::Tensor x, torch::Tensor grad_y, c10::optional<torch::Tensor> gamma, c10::optional<torch::Tensor> beta,
+                                       torch::Tensor mean, torch::Tensor rstd, torch::Tensor group_terms, int64_t groups, bool relu) {
+    CHECK_INPUT(x); CHECK_INPUT(grad_y); CHECK_INPUT(mean); CHECK_INPUT(rstd); CHECK_INPUT(group_terms);
+    TORCH_CHECK(x.sizes() == grad_y.sizes() && x.dim() == 3 && x.size(1) % groups == 0 && group_terms.numel() == 2 * x.size(0) * groups &&
+                group_terms.scalar_type() == x.scalar_type(), "arguments do not match the input");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto dx = torch::empty_like(x);
+    const void* g = gamma.has_value() && gamma->defined() ? gamma->contiguous().data_ptr() : nullptr;
+    const void* b = beta.has_value() && beta->defined() ? beta->contiguous().data_ptr() : nullptr;
+    check(aprnet_groupnorm_backward_apply(dtype_id(x), (int) x.size(0), (int) x.size(1), x.size(2), (int) groups, x.data_ptr(), grad_y.data_ptr(), g, b,
+                                          mean.data_ptr(), rstd.data_ptr(), group_terms.data_ptr(), dx.data_ptr(), relu ? 1 : 0, stream_of(x)), "groupnorm_backward_apply");
+    return dx;
+}
+
 // ---- tree fill on (C, N) tensors -------------------------------------------------------------------
 torch::Tensor fill_tree(APR& apr, torch::Tensor input, bool use_max) {
     CHECK_INPUT(input);
@@ -721,6 +896,7 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
         .def("init_cuda", &APR::init_cuda, "copy access structures to GPU device", "with_tree"_a = true)
         .def("cuda_device_bytes", [](APR& a) { return a.dev ? aprnet_device_bytes(a.dev) : (int64_t) 0; })
         .def("plan", [](APR& a, int dl) { TORCH_CHECK(a.dev, "APR.init_cuda() must be called first");
+                                          c10::cuda::CUDAGuard guard((c10::DeviceIndex) a.dev_index);      // the tables live on the APR's device
                                           check(aprnet_plan_build(a.dev, dl, nullptr), "plan");
                                           if (g_conv_mode == 1) check(aprnet_edge_plan_build(a.dev, dl, nullptr), "edge plan"); }, "level_delta"_a,
              "Build (and cache) the neighbour table of a level delta ahead of the first convolution")
@@ -770,6 +946,15 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
     cuda.def("restrict_kernel333_backward", &restrict_kernel_333_backward, "grad_weights_expanded"_a, "num_levels"_a);
     cuda.def("groupnorm_relu_forward", &groupnorm_relu_forward, "x"_a, "gamma"_a, "beta"_a, "groups"_a, "eps"_a, "relu"_a);
     cuda.def("groupnorm_relu_backward", &groupnorm_relu_backward, "x"_a, "grad_y"_a, "gamma"_a, "beta"_a, "mean"_a, "rstd"_a, "groups"_a, "relu"_a);
+    // split forms for one z-slab of an APR per GPU (halo exchange between the steps, pyapr/aprnet/cuda/sharded.py)
+    cuda.def("conv333_forward_pretree", &conv333_forward_pretree, "aprs"_a, "input"_a, "tree"_a, "weights"_a, "level_delta"_a);
+    cuda.def("conv333_backward_pretree", &conv333_backward_pretree, "aprs"_a, "input"_a, "tree"_a, "kept"_a, "weights"_a, "grad_output"_a, "level_delta"_a, "need_grad_input"_a = true);
+    cuda.def("fill_tree_mean_batch", &fill_tree_mean_batch, "aprs"_a, "input"_a, "level_delta"_a);
+    cuda.def("fill_tree_mean_backward_inplace", &fill_tree_mean_backward_inplace, "aprs"_a, "grad_input"_a, "grad_tree"_a, "level_delta"_a);
+    cuda.def("groupnorm_row_sums", &groupnorm_row_sums, "x"_a);
+    cuda.def("groupnorm_relu_apply", &groupnorm_relu_apply, "x"_a, "gamma"_a, "beta"_a, "mean"_a, "rstd"_a, "groups"_a, "relu"_a);
+    cuda.def("groupnorm_backward_row_sums", &groupnorm_backward_row_sums, "x"_a, "grad_y"_a, "gamma"_a, "beta"_a, "mean"_a, "rstd"_a, "groups"_a, "relu"_a);
+    cuda.def("groupnorm_backward_apply", &groupnorm_backward_apply, "x"_a, "grad_y"_a, "gamma"_a, "beta"_a, "mean"_a, "rstd"_a, "group_terms"_a, "groups"_a, "relu"_a);
     // test / inspection hooks (not part of the reference interface)
     cuda.def("fill_tree_mean", &fill_tree_mean_dl, "apr"_a, "input"_a, "level_delta"_a);
     cuda.def("fill_tree_mean_backward", &fill_tree_mean_dl_backward, "apr"_a, "grad_input"_a, "grad_tree"_a, "level_delta"_a);
@@ -783,8 +968,16 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
     cuda.def("get_conv_precision", []() { return std::string(g_conv_mode == 1 ? "bf16" : "fp32"); });
     cuda.def("tc_error_flag", []() { return aprnet_tc_error_flag(); });
     cuda.def("tc_error_reset", []() { aprnet_tc_error_reset(); }, "Clear the flag that a tensor-core kernel raises when one of its bounded waits runs out");
+    cuda.def("tc_selftest_wait_timeout", [](int max_polls) {
+        check(aprnet_tc_selftest_wait_timeout(max_polls, (void*) at::cuda::getCurrentCUDAStream().stream()), "tc_selftest_wait_timeout");
+    }, "max_polls"_a = 1000, "Test hook: a kernel whose bounded wait runs out and raises the tensor-core error flag");
     cuda.def("tc_set_option", [](const std::string& name, int value) { check(aprnet_tc_set_option(name.c_str(), value), "tc_set_option"); },
              "name"_a, "value"_a, "Switches of the tensor-core kernels ('tma_gather': 1 = source rows by TMA tile::gather4 instead of cp.async)");
+    cuda.def("measure_fp32_fma_tflops", [](int repeats) {
+        double v = 0.0;
+        check(aprnet_measure_fp32_fma_tflops(repeats, &v, (void*) at::cuda::getCurrentCUDAStream().stream()), "measure_fp32_fma_tflops");
+        return v;
+    }, "repeats"_a = 5, "Measured fp32 FMA throughput of the current device in TFLOP/s (register-only FMA chains)");
     cuda.def("profile_enable", [](bool on) { aprnet_profile_enable(on ? 1 : 0); }, "on"_a,
              "Bracket every kernel launch of the library with CUDA events (benchmark use)");
     cuda.def("profile_read", []() {

@@ -84,6 +84,7 @@ struct aprnet_apr {
 };
 
 void aprnet_set_error(const char* fmt, ...);
+int aprnet_check_device(const aprnet_apr* a);      // APRNET_OK when the current device is the handle's device
 
 #define APRNET_CUDA_CHECK(expr)                                                                     \
     do {                                                                                            \
@@ -98,6 +99,9 @@ void aprnet_set_error(const char* fmt, ...);
 
 #define APRNET_ARG_CHECK(cond, msg)                                                                 \
     do { if (!(cond)) { aprnet_set_error("%s: %s", __func__, msg); return APRNET_ERR_ARG; } } while (0)
+
+#define APRNET_DEVICE_CHECK(a)                                                                      \
+    do { const int _rc = aprnet_check_device(a); if (_rc != APRNET_OK) return _rc; } while (0)
 
 inline int aprnet_ceil_div(long long a, long long b) { return (int) ((a + b - 1) / b); }
 
@@ -151,3 +155,7 @@ extern "C" int aprnet_conv333_backward_input_cross_level_tc(aprnet_apr* a, int d
                                                             const void* grows, int gpad, const float* w, float* gin,
                                                             int64_t ld_in, float* gtree, int64_t ld_tree, void* wp_ws,
                                                             void* edge_ws, int64_t edge_ws_bytes, void* stream);
+// same, with the final tree adjoint (grad_tree folded into grad_input) optional
+int aprnet_cross_level_tc(aprnet_apr* a, int dl, int cin, int cout, int slots, const void* grows, int gpad, const float* w, float* gin,
+                          long long ld_in, float* gtree, long long ld_tree, void* wp_ws, void* edge_ws, long long edge_ws_bytes, void* stream,
+                          bool tree_adjoint);

@@ -237,6 +237,9 @@ extern "C" int aprnet_apr_create(aprnet_apr** out, int level_min, int level_max,
                                  const int64_t* tree_row_ptr, const uint16_t* tree_y, int device) {
     APRNET_ARG_CHECK(out && dims && row_ptr && tree_row_ptr, "null argument");
     APRNET_ARG_CHECK(level_min >= 1 && level_max >= level_min && level_max < APRNET_MAX_LEVELS - 1, "bad level range");
+    // the structure is built on `device`; the caller's current device is restored on every way out
+    struct DeviceRestore { int prev = -1; ~DeviceRestore() { if (prev >= 0) cudaSetDevice(prev); } } restore;
+    if (cudaGetDevice(&restore.prev) != cudaSuccess) { restore.prev = -1; cudaGetLastError(); }
     APRNET_CUDA_CHECK(cudaSetDevice(device));
     aprnet_apr* a = new aprnet_apr();
     a->device = device;
@@ -287,12 +290,27 @@ extern "C" int aprnet_apr_create(aprnet_apr** out, int level_min, int level_max,
 
 extern "C" void aprnet_apr_destroy(aprnet_apr* a) {
     if (!a) return;
+    int prev = -1;
+    if (cudaGetDevice(&prev) != cudaSuccess) { prev = -1; cudaGetLastError(); }
     cudaSetDevice(a->device);
     cudaFree(a->row_ptr); cudaFree(a->y); cudaFree(a->tree_row_ptr); cudaFree(a->tree_y);
     cudaFree(a->child); cudaFree(a->tree_scale);
     for (auto& kv : a->plans) cudaFree(kv.second.nbr);
     for (auto& kv : a->edge_plans) aprnet_free_edge_plan(kv.second);
     delete a;
+    if (prev >= 0) cudaSetDevice(prev);
+}
+
+// Every entry point launches on the current device with pointers that live on the handle's device: a mismatch is
+// an argument error here instead of an illegal address inside a kernel.
+int aprnet_check_device(const aprnet_apr* a) {
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess) { cudaGetLastError(); aprnet_set_error("no current CUDA device"); return APRNET_ERR_CUDA; }
+    if (a && cur != a->device) {
+        aprnet_set_error("the access structure lives on device %d but the current device is %d", a->device, cur);
+        return APRNET_ERR_ARG;
+    }
+    return APRNET_OK;
 }
 
 extern "C" int64_t aprnet_number_parts(const aprnet_apr* a, int dl) { return (a && a->valid_dl(dl)) ? a->number_parts(dl) : -1; }
@@ -301,6 +319,7 @@ extern "C" int64_t aprnet_total_tree_nodes(const aprnet_apr* a) { return a ? a->
 extern "C" int64_t aprnet_device_bytes(const aprnet_apr* a) { return a ? a->device_bytes : -1; }
 
 const AprPlan* aprnet_get_plan(aprnet_apr* a, int dl, cudaStream_t stream) {
+    if (aprnet_check_device(a) != APRNET_OK) return nullptr;
     auto it = a->plans.find(dl);
     if (it != a->plans.end()) return &it->second;
     AprPlan p;

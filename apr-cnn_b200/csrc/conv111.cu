@@ -325,6 +325,7 @@ int restrict333(int S, int L, ll filters, const T* src, T* dst, bool backward, c
 extern "C" int aprnet_conv111_forward(const aprnet_apr* a, int dl, int dtype, int cin, int cout, int S, const void* in,
                                       int64_t ld_in, const void* w, void* out, int64_t ld_out, void* stream) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && in && w && out && cin > 0 && cout > 0 && S > 0, "bad argument");
+    APRNET_DEVICE_CHECK(a);
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
     const ll ws = (ll) cin * cout;
@@ -336,6 +337,7 @@ extern "C" int aprnet_conv111_backward_input(const aprnet_apr* a, int dl, int dt
                                              const void* gout, int64_t ld_out, const void* w, void* gin, int64_t ld_in,
                                              void* stream) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && gout && w && gin && cin > 0 && cout > 0 && S > 0, "bad argument");
+    APRNET_DEVICE_CHECK(a);
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
     const ll ws = (ll) cin * cout;
@@ -349,6 +351,7 @@ extern "C" int aprnet_conv111_backward_weights(const aprnet_apr* a, int dl, int 
                                                const void* in, int64_t ld_in, const void* gout, int64_t ld_out,
                                                void* gw, void* partial, void* stream) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && in && gout && gw && partial && cin > 0 && cout > 0 && S > 0, "bad argument");
+    APRNET_DEVICE_CHECK(a);
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
     DISPATCH(dtype, conv111_dw<float>(a, dl, cin, cout, S, (const float*) in, ld_in, (const float*) gout, ld_out, (float*) gw, (float*) partial, st),

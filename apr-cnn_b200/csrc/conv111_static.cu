@@ -97,6 +97,7 @@ extern "C" int aprnet_conv111_backward_weights_static(const aprnet_apr* a, int d
                                                       const float* in, int64_t ld_in, const float* gout, int64_t ld_out,
                                                       float* gw, void* stream) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && in && gout && gw && cin > 0 && cout > 0 && S > 0, "bad argument");
+    APRNET_DEVICE_CHECK(a);
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl), "leading dimension too small");
     const ll elems = (ll) cin * cout;
     if (elems * 4 > STATIC_SCRATCH_ELEMS) {

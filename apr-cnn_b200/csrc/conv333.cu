@@ -319,10 +319,10 @@ int launch_forward(const SegTable& segs, const AprPlan* plan, const T* in, ll ld
 
 template<typename T>
 int conv333_fwd(aprnet_apr* a, int dl, int cin, int cout, int slots, const T* in, ll ld_in, const T* w, T* out, ll ld_out,
-                T* tree, ll ld_tree, cudaStream_t st) {
+                T* tree, ll ld_tree, cudaStream_t st, bool tree_valid = false) {
     const AprPlan* plan = aprnet_get_plan(a, dl, st);
     if (!plan) return APRNET_ERR_CUDA;
-    int rc = aprnet_fill_tree_mean_forward(a, dl, sizeof(T) == 4 ? APRNET_F32 : APRNET_F64, cin, in, ld_in, tree, ld_tree, st);
+    int rc = tree_valid ? APRNET_OK : aprnet_fill_tree_mean_forward(a, dl, sizeof(T) == 4 ? APRNET_F32 : APRNET_F64, cin, in, ld_in, tree, ld_tree, st);
     if (rc) return rc;
     typedef FwdCfg<T> C;
     char pname[64];
@@ -352,7 +352,7 @@ int launch_backward_input(const SegTable& segs, const AprPlan* plan, const T* go
 
 template<typename T>
 int conv333_bwd_input(aprnet_apr* a, int dl, int cin, int cout, int slots, const T* gout, ll ld_out, const T* w, T* gin,
-                      ll ld_in, T* gtree, ll ld_tree, cudaStream_t st, int cross_only = 0) {
+                      ll ld_in, T* gtree, ll ld_tree, cudaStream_t st, int cross_only = 0, bool tree_adjoint = true) {
     const AprPlan* plan = aprnet_get_plan(a, dl, st);
     if (!plan) return APRNET_ERR_CUDA;
     const ll ts = a->tree_size(dl);
@@ -368,6 +368,7 @@ int conv333_bwd_input(aprnet_apr* a, int dl, int cin, int cout, int slots, const
         else rc = launch_backward_input<T, 8, 16, TPB>(segs, plan, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout, st, pname, cross_only);
         if (rc) return rc;
     }
+    if (!tree_adjoint) return APRNET_OK;
     return aprnet_fill_tree_mean_backward(a, dl, sizeof(T) == 4 ? APRNET_F32 : APRNET_F64, cin, gin, ld_in, gtree, ld_tree, st);
 }
 
@@ -458,6 +459,28 @@ extern "C" int aprnet_conv333_backward_input(aprnet_apr* a, int dl, int dtype, i
     cudaStream_t st = (cudaStream_t) stream;
     DISPATCH(dtype, conv333_bwd_input<float>(a, dl, cin, cout, slots, (const float*) gout, ld_out, (const float*) w, (float*) gin, ld_in, (float*) gtree, ld_tree, st),
              conv333_bwd_input<double>(a, dl, cin, cout, slots, (const double*) gout, ld_out, (const double*) w, (double*) gin, ld_in, (double*) gtree, ld_tree, st));
+}
+
+// Split forms for a caller that exchanges tree values between the tree fill and the gather (one z-slab of an
+// APR per GPU): the forward pass takes the tree means as given, the input gradient leaves grad_tree unfolded.
+extern "C" int aprnet_conv333_forward_pretree(aprnet_apr* a, int dl, int dtype, int cin, int cout, int slots, const void* in,
+                                              int64_t ld_in, const void* w, void* out, int64_t ld_out, const void* tree, int64_t ld_tree,
+                                              void* stream) {
+    CONV_CHECKS();
+    APRNET_ARG_CHECK(in && w && out && tree, "null pointer");
+    cudaStream_t st = (cudaStream_t) stream;
+    DISPATCH(dtype, conv333_fwd<float>(a, dl, cin, cout, slots, (const float*) in, ld_in, (const float*) w, (float*) out, ld_out, (float*) tree, ld_tree, st, true),
+             conv333_fwd<double>(a, dl, cin, cout, slots, (const double*) in, ld_in, (const double*) w, (double*) out, ld_out, (double*) tree, ld_tree, st, true));
+}
+
+extern "C" int aprnet_conv333_backward_input_pretree(aprnet_apr* a, int dl, int dtype, int cin, int cout, int slots, const void* gout,
+                                                     int64_t ld_out, const void* w, void* gin, int64_t ld_in, void* gtree,
+                                                     int64_t ld_tree, void* stream) {
+    CONV_CHECKS();
+    APRNET_ARG_CHECK(gout && w && gin && gtree, "null pointer");
+    cudaStream_t st = (cudaStream_t) stream;
+    DISPATCH(dtype, conv333_bwd_input<float>(a, dl, cin, cout, slots, (const float*) gout, ld_out, (const float*) w, (float*) gin, ld_in, (float*) gtree, ld_tree, st, 0, false),
+             conv333_bwd_input<double>(a, dl, cin, cout, slots, (const double*) gout, ld_out, (const double*) w, (double*) gin, ld_in, (double*) gtree, ld_tree, st, 0, false));
 }
 
 extern "C" int64_t aprnet_conv333_partial_elems(int cin, int cout) { return (int64_t) dw_max_ranges(cin, cout) * 27 * cin * cout; }

@@ -597,6 +597,31 @@ int aprnet_tc_pad(int channels) { return pad_to(channels, 16); }
 
 extern "C" int aprnet_tc_error_flag(void) { return g_error_flag_host ? *g_error_flag_host : 0; }
 
+namespace {
+// One thread waits, with the given poll limit, on an mbarrier that nothing arrives at: the wait runs out, the block
+// raises the error flag like the convolution kernels do, and returns.  Exercises the error path without a hang.
+__global__ void wait_timeout_selftest_kernel(unsigned max_polls, int* error_flag) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) { mbar_init(smem_u32(&bar), 1); fence_mbar_init(); }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        bool done = false;
+        for (unsigned it = 0; it < max_polls && !done; ++it) done = mbar_try_wait(smem_u32(&bar), 0);
+        if (!done && error_flag) *error_flag = 1;
+    }
+}
+} // namespace
+
+extern "C" int aprnet_tc_selftest_wait_timeout(int max_polls, void* stream) {
+    APRNET_ARG_CHECK(max_polls > 0 && max_polls <= (1 << 20), "poll limit must be in [1, 2^20]");
+    int rc = ensure_error_flag();
+    if (rc) return rc;
+    wait_timeout_selftest_kernel<<<1, 32, 0, (cudaStream_t) stream>>>((unsigned) max_polls, g_error_flag_dev);
+    APRNET_LAUNCH_CHECK();
+    APRNET_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t) stream));
+    return APRNET_OK;
+}
+
 extern "C" void aprnet_tc_error_reset(void) { if (g_error_flag_host) *g_error_flag_host = 0; }
 
 extern "C" int aprnet_tc_set_option(const char* name, int value) {
@@ -623,13 +648,13 @@ extern "C" int64_t aprnet_conv333_tc_forward_workspace_bytes(const aprnet_apr* a
 }
 
 // forward: out = conv(in) with bf16 operands / fp32 accumulation; tree_scratch receives the fp32 tree means
-extern "C" int aprnet_conv333_forward_tc(aprnet_apr* a, int dl, int cin, int cout, int slots, const float* in, int64_t ld_in,
-                                         const float* w, float* out, int64_t ld_out, float* tree, int64_t ld_tree,
-                                         void* workspace, void* stream) {
+static int conv333_forward_tc_impl(aprnet_apr* a, int dl, int cin, int cout, int slots, const float* in, int64_t ld_in,
+                                   const float* w, float* out, int64_t ld_out, float* tree, int64_t ld_tree,
+                                   void* workspace, void* stream, bool tree_valid) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && cin > 0 && cout > 0 && slots > 0 && in && w && out && tree && workspace, "bad argument");
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl) && ld_tree >= a->tree_size(dl), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
-    int rc = aprnet_fill_tree_mean_forward(a, dl, APRNET_F32, cin, in, ld_in, tree, ld_tree, st);
+    int rc = tree_valid ? APRNET_OK : aprnet_fill_tree_mean_forward(a, dl, APRNET_F32, cin, in, ld_in, tree, ld_tree, st);
     if (rc) return rc;
     const ll n = a->number_parts(dl), t = a->tree_size(dl);
     const int kpad = aprnet_tc_pad(cin);
@@ -645,6 +670,19 @@ extern "C" int aprnet_conv333_forward_tc(aprnet_apr* a, int dl, int cin, int cou
     return aprnet_tc_gather_conv(a, dl, 0, cin, cout, slots, rows, kpad, n, n + t, w, wp, out, ld_out, st);
 }
 
+extern "C" int aprnet_conv333_forward_tc(aprnet_apr* a, int dl, int cin, int cout, int slots, const float* in, int64_t ld_in,
+                                         const float* w, float* out, int64_t ld_out, float* tree, int64_t ld_tree,
+                                         void* workspace, void* stream) {
+    return conv333_forward_tc_impl(a, dl, cin, cout, slots, in, ld_in, w, out, ld_out, tree, ld_tree, workspace, stream, false);
+}
+
+// Split form (see aprnet_conv333_forward_pretree): the tree means are taken as given.
+extern "C" int aprnet_conv333_forward_tc_pretree(aprnet_apr* a, int dl, int cin, int cout, int slots, const float* in, int64_t ld_in,
+                                                 const float* w, float* out, int64_t ld_out, const float* tree, int64_t ld_tree,
+                                                 void* workspace, void* stream) {
+    return conv333_forward_tc_impl(a, dl, cin, cout, slots, in, ld_in, w, out, ld_out, const_cast<float*>(tree), ld_tree, workspace, stream, true);
+}
+
 // Backward pass of the 3x3x3 convolution with the contractions on the tensor cores, from the packed
 // bf16 rows of the input that the forward call left at the start of its workspace
 // (aprnet_conv333_tc_packed_rows_bytes() bytes: particles, tree means, zero row; for Cin <= 4 the same
@@ -653,9 +691,9 @@ extern "C" int aprnet_conv333_forward_tc(aprnet_apr* a, int dl, int cin, int cou
 //   -> cross-level part (per-(target, tap) sums + gather over the targets) and tree adjoint.
 // workspace: aprnet_conv333_tc_workspace_bytes() bytes (its leading part is not touched, so the forward
 // workspace itself may be passed as packed_input_rows).
-extern "C" int aprnet_conv333_backward_tc_rows(aprnet_apr* a, int dl, int cin, int cout, int slots, const void* packed_input_rows,
-                                               const float* gout, int64_t ld_out, const float* w, float* gin, int64_t ld_in, float* gw,
-                                               float* gtree, int64_t ld_tree, float* partial, void* workspace, void* stream) {
+static int conv333_backward_tc_rows_impl(aprnet_apr* a, int dl, int cin, int cout, int slots, const void* packed_input_rows,
+                                         const float* gout, int64_t ld_out, const float* w, float* gin, int64_t ld_in, float* gw,
+                                         float* gtree, int64_t ld_tree, float* partial, void* workspace, void* stream, bool tree_adjoint) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && cin > 0 && cout > 0 && slots > 0 && packed_input_rows && gout && w && gw && gtree && partial && workspace, "bad argument");
     APRNET_ARG_CHECK(ld_out >= a->number_parts(dl) && (!gin || ld_in >= a->number_parts(dl)) && ld_tree >= a->tree_size(dl), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
@@ -672,8 +710,22 @@ extern "C" int aprnet_conv333_backward_tc_rows(aprnet_apr* a, int dl, int cin, i
     if (!gin) return APRNET_OK;          // the caller does not need the input gradient (first layer of a network)
     if ((rc = aprnet_tc_gather_conv(a, dl, 1, cin, cout, slots, grows, gpad, n, n, w, wp, gin, ld_in, st))) return rc;
     void* edge_ws = (char*) wp + aprnet_tc_weight_bytes(cout, cin, slots);
-    return aprnet_conv333_backward_input_cross_level_tc(a, dl, cin, cout, slots, grows, gpad, w, gin, ld_in, gtree, ld_tree, wp, edge_ws,
-                                                        aprnet_edge_workspace_bytes(a, dl, cout), st);
+    return aprnet_cross_level_tc(a, dl, cin, cout, slots, grows, gpad, w, gin, ld_in, gtree, ld_tree, wp, edge_ws,
+                                 aprnet_edge_workspace_bytes(a, dl, cout), st, tree_adjoint);
+}
+
+extern "C" int aprnet_conv333_backward_tc_rows(aprnet_apr* a, int dl, int cin, int cout, int slots, const void* packed_input_rows,
+                                               const float* gout, int64_t ld_out, const float* w, float* gin, int64_t ld_in, float* gw,
+                                               float* gtree, int64_t ld_tree, float* partial, void* workspace, void* stream) {
+    return conv333_backward_tc_rows_impl(a, dl, cin, cout, slots, packed_input_rows, gout, ld_out, w, gin, ld_in, gw, gtree, ld_tree, partial, workspace, stream, true);
+}
+
+// Split form: grad_input holds the direct contributions only and grad_tree the gradient of the tree means; the
+// caller folds them with aprnet_fill_tree_mean_backward after it has exchanged the halo parts.
+extern "C" int aprnet_conv333_backward_tc_rows_pretree(aprnet_apr* a, int dl, int cin, int cout, int slots, const void* packed_input_rows,
+                                                       const float* gout, int64_t ld_out, const float* w, float* gin, int64_t ld_in, float* gw,
+                                                       float* gtree, int64_t ld_tree, float* partial, void* workspace, void* stream) {
+    return conv333_backward_tc_rows_impl(a, dl, cin, cout, slots, packed_input_rows, gout, ld_out, w, gin, ld_in, gw, gtree, ld_tree, partial, workspace, stream, false);
 }
 
 extern "C" int64_t aprnet_conv333_tc_packed_rows_bytes(const aprnet_apr* a, int dl, int cin) {

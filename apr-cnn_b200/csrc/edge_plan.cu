@@ -325,10 +325,9 @@ extern "C" int64_t aprnet_edge_workspace_bytes(const aprnet_apr* a, int dl, int 
 // grad_tree, which the call zero-fills) followed by the tree adjoint.  packed_grad_output_rows:
 // channels-last bf16 dO rows; weights fp32 (slots, Cout, Cin, 27); wp_ws: space for the packed
 // transposed weights; edge_ws: aprnet_edge_workspace_bytes() bytes.
-extern "C" int aprnet_conv333_backward_input_cross_level_tc(aprnet_apr* a, int dl, int cin, int cout, int slots,
-                                                            const void* grows, int gpad, const float* w, float* gin,
-                                                            int64_t ld_in, float* gtree, int64_t ld_tree, void* wp_ws,
-                                                            void* edge_ws, int64_t edge_ws_bytes, void* stream) {
+int aprnet_cross_level_tc(aprnet_apr* a, int dl, int cin, int cout, int slots, const void* grows, int gpad, const float* w, float* gin,
+                          long long ld_in, float* gtree, long long ld_tree, void* wp_ws, void* edge_ws, long long edge_ws_bytes, void* stream,
+                          bool tree_adjoint) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && cin > 0 && cout > 0 && slots > 0 && grows && w && gin && gtree && wp_ws && edge_ws, "bad argument");
     APRNET_ARG_CHECK(gpad == aprnet_tc_pad(cout), "packed row width does not match the padded channel count");
     cudaStream_t st = (cudaStream_t) stream;
@@ -363,5 +362,13 @@ extern "C" int aprnet_conv333_backward_input_cross_level_tc(aprnet_apr* a, int d
             k0 = k1;
         }
     }
+    if (!tree_adjoint) return APRNET_OK;
     return aprnet_fill_tree_mean_backward(a, dl, APRNET_F32, cin, gin, ld_in, gtree, ld_tree, st);
+}
+
+extern "C" int aprnet_conv333_backward_input_cross_level_tc(aprnet_apr* a, int dl, int cin, int cout, int slots,
+                                                            const void* grows, int gpad, const float* w, float* gin,
+                                                            int64_t ld_in, float* gtree, int64_t ld_tree, void* wp_ws,
+                                                            void* edge_ws, int64_t edge_ws_bytes, void* stream) {
+    return aprnet_cross_level_tc(a, dl, cin, cout, slots, grows, gpad, w, gin, ld_in, gtree, ld_tree, wp_ws, edge_ws, edge_ws_bytes, stream, true);
 }

@@ -242,3 +242,95 @@ extern "C" int aprnet_groupnorm_relu_backward(int dtype, int batch, int channels
     aprnet_set_error("aprnet_groupnorm_relu_backward: unknown dtype %d", dtype);
     return APRNET_ERR_ARG;
 }
+
+// ---- split forms: the caller combines the sums of several devices before the statistics are applied --------
+// (one z-slab of an APR per GPU: every rank sums over the particles it owns, the sums are all-reduced, every rank
+// applies the same mean / rstd).  row_sums: double [batch * channels][2].
+template<typename T>
+static int gn_row_sums(int B, int C, ll n, const T* x, double* ws, double* row_sums, cudaStream_t st) {
+    const ll rows = (ll) B * C;
+    const int nchunks = gn_chunks(n, rows);
+    const ll chunk_len = (n + nchunks - 1) / nchunks;
+    { AprnetProfScope _p("groupnorm_stats", st);
+    gn_partial_stats_kernel<T><<<dim3(nchunks, (unsigned) rows), GN_TPB, 0, st>>>(x, n, chunk_len, ws, nchunks);
+    gn_backward_rows_kernel<<<aprnet_ceil_div(rows, 128), 128, 0, st>>>(ws, nchunks, rows, row_sums);
+    }
+    APRNET_LAUNCH_CHECK();
+    return APRNET_OK;
+}
+
+template<typename T>
+static int gn_apply(int B, int C, ll n, int groups, const T* x, const T* gamma, const T* beta, const T* mean, const T* rstd, T* y, int relu, cudaStream_t st) {
+    const ll rows = (ll) B * C;
+    const int gx = (int) std::max<ll>(1, std::min<ll>((n + GN_TPB * 8 - 1) / (GN_TPB * 8), 4096));
+    { AprnetProfScope _p("groupnorm_relu_apply", st);
+    gn_relu_apply_kernel<T><<<dim3(gx, (unsigned) rows), GN_TPB, 0, st>>>(x, n, C, C / groups, gamma, beta, mean, rstd, y, relu);
+    }
+    APRNET_LAUNCH_CHECK();
+    return APRNET_OK;
+}
+
+template<typename T>
+static int gn_bwd_row_sums(int B, int C, ll n, int groups, const T* x, const T* dy, const T* gamma, const T* beta, const T* mean, const T* rstd,
+                           double* ws, double* row_sums, int relu, cudaStream_t st) {
+    const ll rows = (ll) B * C;
+    const int nchunks = gn_chunks(n, rows);
+    const ll chunk_len = (n + nchunks - 1) / nchunks;
+    { AprnetProfScope _p("groupnorm_bwd_reduce", st);
+    gn_backward_partial_kernel<T><<<dim3(nchunks, (unsigned) rows), GN_TPB, 0, st>>>(x, dy, n, chunk_len, C, C / groups, gamma, beta, mean, rstd, ws, nchunks, relu);
+    gn_backward_rows_kernel<<<aprnet_ceil_div(rows, 128), 128, 0, st>>>(ws, nchunks, rows, row_sums);
+    }
+    APRNET_LAUNCH_CHECK();
+    return APRNET_OK;
+}
+
+template<typename T>
+static int gn_bwd_apply(int B, int C, ll n, int groups, const T* x, const T* dy, const T* gamma, const T* beta, const T* mean, const T* rstd,
+                        const T* group_terms, T* dx, int relu, cudaStream_t st) {
+    const ll rows = (ll) B * C;
+    const int gx = (int) std::max<ll>(1, std::min<ll>((n + GN_TPB * 8 - 1) / (GN_TPB * 8), 4096));
+    { AprnetProfScope _p("groupnorm_bwd_apply", st);
+    gn_backward_apply_kernel<T><<<dim3(gx, (unsigned) rows), GN_TPB, 0, st>>>(x, dy, n, C, C / groups, gamma, beta, mean, rstd, group_terms, dx, relu);
+    }
+    APRNET_LAUNCH_CHECK();
+    return APRNET_OK;
+}
+
+#define GN_DISPATCH(F32_CALL, F64_CALL)                                               \
+    if (dtype == APRNET_F32) return F32_CALL;                                         \
+    if (dtype == APRNET_F64) return F64_CALL;                                         \
+    aprnet_set_error("%s: unknown dtype %d", __func__, dtype);                       \
+    return APRNET_ERR_ARG;
+
+extern "C" int aprnet_groupnorm_row_sums(int dtype, int batch, int channels, int64_t n, const void* x, void* workspace, double* row_sums, void* stream) {
+    APRNET_ARG_CHECK(batch > 0 && channels > 0 && n > 0 && x && workspace && row_sums, "bad argument");
+    cudaStream_t st = (cudaStream_t) stream;
+    GN_DISPATCH(gn_row_sums<float>(batch, channels, n, (const float*) x, (double*) workspace, row_sums, st),
+                gn_row_sums<double>(batch, channels, n, (const double*) x, (double*) workspace, row_sums, st))
+}
+
+extern "C" int aprnet_groupnorm_relu_apply(int dtype, int batch, int channels, int64_t n, int groups, const void* x, const void* gamma, const void* beta,
+                                           const void* mean, const void* rstd, void* y, int relu, void* stream) {
+    APRNET_ARG_CHECK(batch > 0 && channels > 0 && n > 0 && groups > 0 && channels % groups == 0 && x && y && mean && rstd, "bad argument");
+    cudaStream_t st = (cudaStream_t) stream;
+    GN_DISPATCH(gn_apply<float>(batch, channels, n, groups, (const float*) x, (const float*) gamma, (const float*) beta, (const float*) mean, (const float*) rstd, (float*) y, relu, st),
+                gn_apply<double>(batch, channels, n, groups, (const double*) x, (const double*) gamma, (const double*) beta, (const double*) mean, (const double*) rstd, (double*) y, relu, st))
+}
+
+extern "C" int aprnet_groupnorm_backward_row_sums(int dtype, int batch, int channels, int64_t n, int groups, const void* x, const void* grad_y,
+                                                  const void* gamma, const void* beta, const void* mean, const void* rstd, void* workspace,
+                                                  double* row_sums, int relu, void* stream) {
+    APRNET_ARG_CHECK(batch > 0 && channels > 0 && n > 0 && groups > 0 && channels % groups == 0 && x && grad_y && mean && rstd && workspace && row_sums, "bad argument");
+    cudaStream_t st = (cudaStream_t) stream;
+    GN_DISPATCH(gn_bwd_row_sums<float>(batch, channels, n, groups, (const float*) x, (const float*) grad_y, (const float*) gamma, (const float*) beta, (const float*) mean, (const float*) rstd, (double*) workspace, row_sums, relu, st),
+                gn_bwd_row_sums<double>(batch, channels, n, groups, (const double*) x, (const double*) grad_y, (const double*) gamma, (const double*) beta, (const double*) mean, (const double*) rstd, (double*) workspace, row_sums, relu, st))
+}
+
+extern "C" int aprnet_groupnorm_backward_apply(int dtype, int batch, int channels, int64_t n, int groups, const void* x, const void* grad_y,
+                                               const void* gamma, const void* beta, const void* mean, const void* rstd, const void* group_terms,
+                                               void* grad_x, int relu, void* stream) {
+    APRNET_ARG_CHECK(batch > 0 && channels > 0 && n > 0 && groups > 0 && channels % groups == 0 && x && grad_y && mean && rstd && group_terms && grad_x, "bad argument");
+    cudaStream_t st = (cudaStream_t) stream;
+    GN_DISPATCH(gn_bwd_apply<float>(batch, channels, n, groups, (const float*) x, (const float*) grad_y, (const float*) gamma, (const float*) beta, (const float*) mean, (const float*) rstd, (const float*) group_terms, (float*) grad_x, relu, st),
+                gn_bwd_apply<double>(batch, channels, n, groups, (const double*) x, (const double*) grad_y, (const double*) gamma, (const double*) beta, (const double*) mean, (const double*) rstd, (const double*) group_terms, (double*) grad_x, relu, st))
+}

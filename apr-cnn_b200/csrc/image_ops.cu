@@ -109,6 +109,7 @@ int run_levels(const aprnet_apr* a, int dl, int C, T* parts, ll ld, T* image, in
 template<bool TO_IMAGE>
 int dispatch(const aprnet_apr* a, int dl, int dtype, int C, void* parts, ll ld, void* image, int mean, void* stream) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && C > 0 && parts && image, "bad argument");
+    APRNET_DEVICE_CHECK(a);
     APRNET_ARG_CHECK(ld >= a->number_parts(dl), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
     if (dtype == APRNET_F32) return run_levels<float, TO_IMAGE>(a, dl, C, (float*) parts, ld, (float*) image, mean, st);

@@ -334,6 +334,7 @@ int upsample_impl(const aprnet_apr* a, int dl, int C, const T* src, ll ld_src, T
 extern "C" int aprnet_fill_tree_mean_forward(const aprnet_apr* a, int dl, int dtype, int C, const void* in, int64_t ld_in,
                                              void* tree, int64_t ld_tree, void* stream) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && in && tree && C > 0, "bad argument");
+    APRNET_DEVICE_CHECK(a);
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_tree >= a->tree_size(dl), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
     DISPATCH(dtype, fill_tree_mean_fwd<float>(a, dl, C, (const float*) in, ld_in, (float*) tree, ld_tree, st),
@@ -348,6 +349,7 @@ extern "C" int aprnet_fill_tree_mean_full(const aprnet_apr* a, int dtype, int C,
 extern "C" int aprnet_fill_tree_mean_backward(const aprnet_apr* a, int dl, int dtype, int C, void* gin, int64_t ld_in,
                                               void* gtree, int64_t ld_tree, void* stream) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && gin && gtree && C > 0, "bad argument");
+    APRNET_DEVICE_CHECK(a);
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_tree >= a->tree_size(dl), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
     DISPATCH(dtype, fill_tree_mean_bwd<float>(a, dl, C, (float*) gin, ld_in, (float*) gtree, ld_tree, st),
@@ -357,6 +359,7 @@ extern "C" int aprnet_fill_tree_mean_backward(const aprnet_apr* a, int dl, int d
 extern "C" int aprnet_fill_tree_max(const aprnet_apr* a, int dtype, int C, const void* in, int64_t ld_in, void* tree,
                                     int64_t ld_tree, void* stream) {
     APRNET_ARG_CHECK(a && in && tree && C > 0, "bad argument");
+    APRNET_DEVICE_CHECK(a);
     APRNET_ARG_CHECK(ld_in >= a->n_particles && ld_tree >= a->n_tree, "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
     DISPATCH(dtype, fill_tree_max_impl<float>(a, C, (const float*) in, ld_in, (float*) tree, ld_tree, st),
@@ -366,6 +369,7 @@ extern "C" int aprnet_fill_tree_max(const aprnet_apr* a, int dtype, int C, const
 extern "C" int aprnet_maxpool_forward(const aprnet_apr* a, int dl, int dtype, int C, const void* in, int64_t ld_in,
                                       void* out, int64_t* idx, int64_t ld_out, void* stream) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && a->valid_dl(dl + 1) && in && out && idx && C > 0, "bad argument");
+    APRNET_DEVICE_CHECK(a);
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl + 1), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
     DISPATCH(dtype, maxpool_fwd<float>(a, dl, C, (const float*) in, ld_in, (float*) out, (long long*) idx, ld_out, st),
@@ -375,6 +379,7 @@ extern "C" int aprnet_maxpool_forward(const aprnet_apr* a, int dl, int dtype, in
 extern "C" int aprnet_maxpool_backward(const aprnet_apr* a, int dl, int dtype, int C, const void* gout, const int64_t* idx,
                                        int64_t ld_out, void* gin, int64_t ld_in, void* stream) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && a->valid_dl(dl + 1) && gout && gin && idx && C > 0, "bad argument");
+    APRNET_DEVICE_CHECK(a);
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl + 1), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
     DISPATCH(dtype, maxpool_bwd<float>(a, dl, C, (const float*) gout, (const long long*) idx, ld_out, (float*) gin, ld_in, st),
@@ -384,6 +389,7 @@ extern "C" int aprnet_maxpool_backward(const aprnet_apr* a, int dl, int dtype, i
 extern "C" int aprnet_upsample_forward(const aprnet_apr* a, int dl, int dtype, int C, const void* in, int64_t ld_in, void* out,
                                        int64_t ld_out, void* stream) {
     APRNET_ARG_CHECK(a && dl > 0 && a->valid_dl(dl) && in && out && C > 0, "bad argument (level_delta must be > 0)");
+    APRNET_DEVICE_CHECK(a);
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl - 1), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
     DISPATCH(dtype, (upsample_impl<float, false>(a, dl, C, (const float*) in, ld_in, (float*) out, ld_out, st)),
@@ -393,6 +399,7 @@ extern "C" int aprnet_upsample_forward(const aprnet_apr* a, int dl, int dtype, i
 extern "C" int aprnet_upsample_backward(const aprnet_apr* a, int dl, int dtype, int C, const void* gout, int64_t ld_out,
                                         void* gin, int64_t ld_in, void* stream) {
     APRNET_ARG_CHECK(a && dl > 0 && a->valid_dl(dl) && gout && gin && C > 0, "bad argument (level_delta must be > 0)");
+    APRNET_DEVICE_CHECK(a);
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl - 1), "leading dimension too small");
     cudaStream_t st = (cudaStream_t) stream;
     DISPATCH(dtype, (upsample_impl<float, true>(a, dl, C, (const float*) gout, ld_out, (float*) gin, ld_in, st)),

@@ -47,6 +47,10 @@ const char* aprnet_last_error(void);
  * records and returns the untruncated length.  Not thread-safe; meant for benchmarks. */
 void aprnet_profile_enable(int on);
 int64_t aprnet_profile_read(char* buf, int64_t buflen);
+/* Measured fp32 multiply-add throughput of the current device in TFLOP/s (best of `repeats` short runs of
+ * register-only FMA chains, timed with CUDA events): the denominator of the roofline of the fp32 CUDA-core
+ * convolution path.  No counterpart in the reference. */
+int aprnet_measure_fp32_fma_tflops(int repeats, double* tflops_out, void* stream);
 
 /* ---- access structure ------------------------------------------------------------------------
  * Replaces LibAPR's APR::init_cuda / gpuAPRHelper / gpuTreeHelper as used at
@@ -127,6 +131,21 @@ int aprnet_conv333_backward_weights(aprnet_apr* apr, int level_delta, int dtype,
                                     const void* grad_output, int64_t ld_out, void* grad_weights,
                                     void* partial, void* stream);
 
+/* Split forms for a caller that exchanges values between the tree fill and the gather -- one z-slab of an
+ * APR per GPU with halo rows from the neighbouring slabs (the reference has no multi-GPU path; the stencil
+ * reach that fixes the halo is pyapr/aprnet/cuda/src/conv333_gpu.cu:65-72,239-246).  Forward: `tree` holds
+ * the tree means (aprnet_fill_tree_mean_forward, then the halo entries from their owners) and is only
+ * read.  Backward: grad_input receives the direct contributions only and grad_tree the gradient of the
+ * tree means; the caller adds the halo parts at their owners and then folds grad_tree into grad_input with
+ * aprnet_fill_tree_mean_backward.  Same argument conventions as the calls above. */
+int aprnet_conv333_forward_pretree(aprnet_apr* apr, int level_delta, int dtype, int cin, int cout, int num_slots,
+                                   const void* input, int64_t ld_in, const void* weights,
+                                   void* output, int64_t ld_out, const void* tree, int64_t ld_tree, void* stream);
+int aprnet_conv333_backward_input_pretree(aprnet_apr* apr, int level_delta, int dtype, int cin, int cout, int num_slots,
+                                          const void* grad_output, int64_t ld_out, const void* weights,
+                                          void* grad_input, int64_t ld_in, void* grad_tree, int64_t ld_tree,
+                                          void* stream);
+
 /* ---- 3x3x3 convolution on the tensor cores (bf16 operands, fp32 accumulation) ------------------
  * No counterpart in the reference (its kernels are CUDA-core only).  Same contract as
  * aprnet_conv333_forward for float32 tensors; results differ by the bf16 rounding of inputs and
@@ -160,6 +179,14 @@ int aprnet_conv333_backward_tc_rows(aprnet_apr* apr, int level_delta, int cin, i
                                     const void* packed_input_rows, const float* grad_output, int64_t ld_out,
                                     const float* weights, float* grad_input, int64_t ld_in, float* grad_weights,
                                     float* grad_tree_scratch, int64_t ld_tree, float* partial, void* workspace, void* stream);
+/* Split forms on the tensor cores (see aprnet_conv333_forward_pretree). */
+int aprnet_conv333_forward_tc_pretree(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
+                                      const float* input, int64_t ld_in, const float* weights, float* output, int64_t ld_out,
+                                      const float* tree, int64_t ld_tree, void* workspace, void* stream);
+int aprnet_conv333_backward_tc_rows_pretree(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
+                                            const void* packed_input_rows, const float* grad_output, int64_t ld_out,
+                                            const float* weights, float* grad_input, int64_t ld_in, float* grad_weights,
+                                            float* grad_tree, int64_t ld_tree, float* partial, void* workspace, void* stream);
 /* Building blocks of the above, exported for callers that keep the packed copies around. */
 int aprnet_conv333_backward_weights_tc(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
                                        const void* packed_input_rows, int input_row_width,
@@ -182,6 +209,9 @@ int aprnet_conv333_backward_input_cross_level_tc(aprnet_apr* apr, int level_delt
 int aprnet_tc_error_flag(void);
 /* Clears the flag above so that the tensor-core entry points accept calls again after a wait ran out. */
 void aprnet_tc_error_reset(void);
+/* Test hook for the error path: launches one small kernel whose bounded wait (max_polls polls) is on a barrier
+ * that nothing arrives at; the wait runs out, the kernel raises the flag above and returns (nothing hangs). */
+int aprnet_tc_selftest_wait_timeout(int max_polls, void* stream);
 /* Switches of the tensor-core kernels.  "tma_gather": 1 makes the forward and same-level input-gradient
  * kernels fetch their source rows with TMA tile::gather4 copies through a tensor map of the packed rows
  * instead of 16-byte cp.async copies (same results; default 0). */
@@ -233,6 +263,23 @@ int aprnet_groupnorm_relu_backward(int dtype, int batch, int channels, int64_t n
                                    const void* grad_y, const void* gamma, const void* beta, const void* mean,
                                    const void* rstd, void* grad_x, void* grad_gamma, void* grad_beta,
                                    void* workspace, int relu, void* stream);
+
+/* Split forms of the two passes above for one z-slab of an APR per GPU: every rank reduces over the
+ * particles it owns into row_sums (double, (batch * channels, 2): sum x and sum x^2 forward; sum dy_eff and
+ * sum dy_eff * xhat backward), the caller all-reduces the sums, derives mean / rstd / the two group terms
+ * (means of gamma * dy_eff and of gamma * dy_eff * xhat over the group) and applies them.  No counterpart in
+ * the reference (it has no multi-GPU path). */
+int aprnet_groupnorm_row_sums(int dtype, int batch, int channels, int64_t n, const void* x, void* workspace,
+                              double* row_sums, void* stream);
+int aprnet_groupnorm_relu_apply(int dtype, int batch, int channels, int64_t n, int groups, const void* x,
+                                const void* gamma, const void* beta, const void* mean, const void* rstd, void* y,
+                                int relu, void* stream);
+int aprnet_groupnorm_backward_row_sums(int dtype, int batch, int channels, int64_t n, int groups, const void* x,
+                                       const void* grad_y, const void* gamma, const void* beta, const void* mean,
+                                       const void* rstd, void* workspace, double* row_sums, int relu, void* stream);
+int aprnet_groupnorm_backward_apply(int dtype, int batch, int channels, int64_t n, int groups, const void* x,
+                                    const void* grad_y, const void* gamma, const void* beta, const void* mean,
+                                    const void* rstd, const void* group_terms, void* grad_x, int relu, void* stream);
 
 /* ---- max pooling / constant up-sampling --------------------------------------------------------
  * pyapr/aprnet/cuda/src/maxpool_gpu.hpp:24-40, upsample_constant_gpu.hpp:17-31.
