@@ -17,7 +17,9 @@ What differs from the single-GPU modules:
   boundary (halo entries carry values that the next exchange overwrites).
 
 Invariants the modules keep: halo entries of every 3x3x3 convolution output and of every GroupNorm input are
-zero; halo entries of every activation gradient are cleared in place when a module of this file receives it.
+zero; halo entries of every activation gradient are cleared in place when a module of this file receives it,
+and the gradients these modules return are zero at halo entries (so the unchanged modules between them -- 1x1x1
+convolution, pooling, up-sampling, concatenation -- never see a contribution from a location the rank does not own).
 """
 import types
 
@@ -175,6 +177,7 @@ class ShardedGroupNormReLUFunction(Function):
         shard.all_reduce(terms)
         terms = (terms / ctx.m).to(x.dtype).contiguous()
         dx = B.gn_backward_apply(x, grad_y, weight, bias, mean, rstd, terms, groups, ctx.relu)
+        shard.halo.zero_halo(ctx.dl, dx)                     # the mean terms are non-zero everywhere; halo gradients must stay zero
         dgamma = rs[:, 1].to(x.dtype) if weight is not None else None
         dbeta = rs[:, 0].to(x.dtype) if bias is not None else None
         return dx, dgamma, dbeta, None, None, None, None
