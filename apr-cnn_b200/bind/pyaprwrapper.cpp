@@ -139,6 +139,14 @@ namespace {
 // 0 = exact fp32/fp64 CUDA-core kernels; 1 = bf16 tensor-core path for float32 3x3x3 convolutions
 int g_conv_mode = 0;
 
+// arithmetic of one call: "" = the process-wide setting, "fp32" / "bf16" = this call only (per-module option)
+inline int resolve_mode(const std::string& precision) {
+    if (precision.empty()) return g_conv_mode;
+    if (precision == "fp32") return 0;
+    if (precision == "bf16") return 1;
+    throw std::invalid_argument("precision must be '', 'fp32' or 'bf16'");
+}
+
 inline void check(int rc, const char* what) {
     TORCH_CHECK(rc == APRNET_OK, what, " failed (", rc, "): ", aprnet_last_error());
 }
@@ -181,7 +189,8 @@ inline void zero_padding(torch::Tensor& t, int64_t b, int64_t valid) {
 }
 
 // ---- 3x3x3 convolution ------------------------------------------------------------------------
-static std::vector<torch::Tensor> conv333_forward_impl(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights, torch::Tensor level_delta, bool keep_tree) {
+static std::vector<torch::Tensor> conv333_forward_impl(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights, torch::Tensor level_delta, bool keep_tree,
+                                                       const std::string& precision = "") {
     CHECK_INPUT(input); CHECK_INPUT(weights);
     check_batch(aprs, input);
     TORCH_CHECK(weights.dim() == 6 && weights.size(3) == 3 && weights.size(4) == 3 && weights.size(5) == 3, "weights must be (levels, Cout, Cin, 3, 3, 3)");
@@ -200,7 +209,7 @@ static std::vector<torch::Tensor> conv333_forward_impl(std::vector<APR*>& aprs, 
     // one tree buffer per batch item when the caller keeps it for the backward pass, else one shared scratch
     auto tree_all = torch::empty({keep_tree ? input.size(0) : 1, cin, max_tree}, input.options());
     const int dt = dtype_id(input);
-    const bool tc = g_conv_mode == 1 && dt == APRNET_F32;
+    const bool tc = resolve_mode(precision) == 1 && dt == APRNET_F32;
     torch::Tensor ws;
     if (tc) {
         int64_t bytes = 256;
@@ -228,8 +237,9 @@ torch::Tensor conv333_forward(std::vector<APR*>& aprs, torch::Tensor input, torc
 }
 
 // same, but also returns the tree means (B, Cin, T) so that the backward pass need not recompute them
-std::vector<torch::Tensor> conv333_forward_keep_tree(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights, torch::Tensor level_delta) {
-    return conv333_forward_impl(aprs, input, weights, level_delta, true);
+std::vector<torch::Tensor> conv333_forward_keep_tree(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights, torch::Tensor level_delta,
+                                                     const std::string& precision) {
+    return conv333_forward_impl(aprs, input, weights, level_delta, true, precision);
 }
 
 // Tensor-core forward that keeps the packed bf16 rows of the input (particles, tree means, zero row) for the
@@ -301,7 +311,7 @@ std::vector<torch::Tensor> conv333_backward_with_rows(std::vector<APR*>& aprs, t
 
 static std::vector<torch::Tensor> conv333_backward_impl(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights,
                                             torch::Tensor grad_output, torch::Tensor level_delta, c10::optional<torch::Tensor> saved_tree,
-                                            bool need_grad_input = true) {
+                                            bool need_grad_input = true, const std::string& precision = "") {
     CHECK_INPUT(input); CHECK_INPUT(weights); CHECK_INPUT(grad_output);
     check_batch(aprs, input);
     TORCH_CHECK(grad_output.dim() == 3 && grad_output.size(0) == input.size(0) && grad_output.size(1) == weights.size(1) &&
@@ -317,7 +327,7 @@ static std::vector<torch::Tensor> conv333_backward_impl(std::vector<APR*>& aprs,
     const int64_t cin = input.size(1), cout = weights.size(1), n = input.size(2);
     const int dt = dtype_id(input);
     void* st = stream_of(input);
-    const bool tc = g_conv_mode == 1 && dt == APRNET_F32;
+    const bool tc = resolve_mode(precision) == 1 && dt == APRNET_F32;
     const bool skip_gin = tc && !need_grad_input;        // only the tensor-core driver can leave the input gradient out
     const bool have_tree = saved_tree.has_value() && saved_tree->defined() && saved_tree->dim() == 3 && saved_tree->size(0) == input.size(0) &&
                            saved_tree->size(1) == cin && saved_tree->size(2) == max_tree && saved_tree->is_contiguous() &&
@@ -370,14 +380,14 @@ std::vector<torch::Tensor> conv333_backward(std::vector<APR*>& aprs, torch::Tens
 
 std::vector<torch::Tensor> conv333_backward_with_tree(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights,
                                                       torch::Tensor grad_output, torch::Tensor level_delta, torch::Tensor tree,
-                                                      bool need_grad_input) {
-    return conv333_backward_impl(aprs, input, weights, grad_output, level_delta, tree, need_grad_input);
+                                                      bool need_grad_input, const std::string& precision) {
+    return conv333_backward_impl(aprs, input, weights, grad_output, level_delta, tree, need_grad_input, precision);
 }
 
 // ---- 3x3x3 convolution, split forms for one z-slab of an APR per GPU (pyapr/aprnet/cuda/sharded.py) ----------
 // forward with given tree means (B, Cin, T); returns {output, kept}: kept = packed bf16 rows (bf16 mode) or an empty tensor
 std::vector<torch::Tensor> conv333_forward_pretree(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor tree, torch::Tensor weights,
-                                                   torch::Tensor level_delta) {
+                                                   torch::Tensor level_delta, const std::string& precision) {
     CHECK_INPUT(input); CHECK_INPUT(weights); CHECK_INPUT(tree);
     check_batch(aprs, input);
     TORCH_CHECK(weights.dim() == 6 && weights.size(3) == 3 && weights.size(4) == 3 && weights.size(5) == 3, "weights must be (levels, Cout, Cin, 3, 3, 3)");
@@ -388,7 +398,7 @@ std::vector<torch::Tensor> conv333_forward_pretree(std::vector<APR*>& aprs, torc
     const auto dl = read_level_delta(level_delta, aprs.size());
     const int64_t cin = input.size(1), cout = weights.size(1), n = input.size(2), ldt = tree.size(2);
     const int dt = dtype_id(input);
-    const bool tc = g_conv_mode == 1 && dt == APRNET_F32;
+    const bool tc = resolve_mode(precision) == 1 && dt == APRNET_F32;
     int64_t rows_bytes = 256, w_bytes = 256;
     for (size_t i = 0; i < aprs.size(); ++i) {
         check_level_delta(*aprs[i], dl[i]);
@@ -425,7 +435,7 @@ std::vector<torch::Tensor> conv333_backward_pretree(std::vector<APR*>& aprs, tor
     const auto dl = read_level_delta(level_delta, aprs.size());
     const int64_t cin = weights.size(2), cout = weights.size(1), n = grad_output.size(2), ldt = tree.size(2), B = grad_output.size(0);
     const int dt = dtype_id(grad_output);
-    const bool tc = g_conv_mode == 1 && dt == APRNET_F32 && kept.numel() > 0;
+    const bool tc = dt == APRNET_F32 && kept.numel() > 0;          // a rows buffer exists only when the forward call ran on the tensor cores
     TORCH_CHECK(grad_output.size(1) == cout && tree.dim() == 3 && tree.size(0) == B && tree.size(1) == cin, "shapes do not match");
     if (!tc) { CHECK_INPUT(input); TORCH_CHECK(input.dim() == 3 && input.size(1) == cin && input.size(2) == n, "input shape does not match"); }
     auto grad_tree = torch::zeros({B, cin, ldt}, grad_output.options());
@@ -932,8 +942,9 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
     cuda.def("conv333_forward", &conv333_forward, "aprs"_a, "input"_a, "weights"_a, "level_delta"_a);
     cuda.def("conv333_backward", &conv333_backward, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a);
     // extensions: keep the tree means of the forward pass for the backward pass
-    cuda.def("conv333_forward_keep_tree", &conv333_forward_keep_tree, "aprs"_a, "input"_a, "weights"_a, "level_delta"_a);
-    cuda.def("conv333_backward_with_tree", &conv333_backward_with_tree, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a, "tree"_a, "need_grad_input"_a = true);
+    cuda.def("conv333_forward_keep_tree", &conv333_forward_keep_tree, "aprs"_a, "input"_a, "weights"_a, "level_delta"_a, "precision"_a = "");
+    cuda.def("conv333_backward_with_tree", &conv333_backward_with_tree, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a, "tree"_a, "need_grad_input"_a = true,
+             "precision"_a = "");
     cuda.def("conv333_forward_keep_rows", &conv333_forward_keep_rows, "aprs"_a, "input"_a, "weights"_a, "level_delta"_a);
     cuda.def("conv333_backward_with_rows", &conv333_backward_with_rows, "aprs"_a, "rows"_a, "weights"_a, "grad_output"_a, "level_delta"_a, "need_grad_input"_a = true);
     cuda.def("upsample_const_forward", &upsample_const_forward, "aprs"_a, "input"_a, "level_delta"_a);
@@ -947,7 +958,7 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
     cuda.def("groupnorm_relu_forward", &groupnorm_relu_forward, "x"_a, "gamma"_a, "beta"_a, "groups"_a, "eps"_a, "relu"_a);
     cuda.def("groupnorm_relu_backward", &groupnorm_relu_backward, "x"_a, "grad_y"_a, "gamma"_a, "beta"_a, "mean"_a, "rstd"_a, "groups"_a, "relu"_a);
     // split forms for one z-slab of an APR per GPU (halo exchange between the steps, pyapr/aprnet/cuda/sharded.py)
-    cuda.def("conv333_forward_pretree", &conv333_forward_pretree, "aprs"_a, "input"_a, "tree"_a, "weights"_a, "level_delta"_a);
+    cuda.def("conv333_forward_pretree", &conv333_forward_pretree, "aprs"_a, "input"_a, "tree"_a, "weights"_a, "level_delta"_a, "precision"_a = "");
     cuda.def("conv333_backward_pretree", &conv333_backward_pretree, "aprs"_a, "input"_a, "tree"_a, "kept"_a, "weights"_a, "grad_output"_a, "level_delta"_a, "need_grad_input"_a = true);
     cuda.def("fill_tree_mean_batch", &fill_tree_mean_batch, "aprs"_a, "input"_a, "level_delta"_a);
     cuda.def("fill_tree_mean_backward_inplace", &fill_tree_mean_backward_inplace, "aprs"_a, "grad_input"_a, "grad_tree"_a, "level_delta"_a);

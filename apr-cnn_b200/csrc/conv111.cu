@@ -31,13 +31,23 @@ inline SegTable make_seg_table(const std::vector<Segment>& segs, int tile) {
     return t;
 }
 
+// 16-byte vector of T (4 floats / 2 doubles): the staged weights are read from shared memory in such pieces, so that
+// one shared-memory instruction feeds several multiply-adds (with scalar reads the kernel is bound by the
+// shared-memory pipe, one broadcast read per multiply-add).
+template<typename T> struct Vec16;
+template<> struct Vec16<float> { typedef float4 type; static constexpr int N = 4; };
+template<> struct Vec16<double> { typedef double2 type; static constexpr int N = 2; };
+
 // out[o][p] = sum_i w[slot][o][i] * in[i][p]; weight element (s, o, i) at w[s*ws + o*wo + i*wi]
 // (forward: wo = Cin, wi = 1; input gradient: roles of the channel axes swapped, wo = 1, wi = Cin_fwd).
 template<typename T, int OB, int TPB>
 __global__ void __launch_bounds__(TPB) conv111_kernel(SegTable segs, const T* __restrict__ in, ll ld_in,
                                                       const T* __restrict__ w, ll ws, ll wo, ll wi,
                                                       T* __restrict__ out, ll ld_out, int n_in, int n_out) {
-    extern __shared__ unsigned char smem_raw[];
+    typedef typename Vec16<T>::type V;
+    constexpr int VN = Vec16<T>::N;
+    static_assert(OB % VN == 0, "output block is a whole number of 16-byte vectors");
+    extern __shared__ __align__(16) unsigned char smem_raw[];
     T* wsm = reinterpret_cast<T*>(smem_raw);              // [n_in][OB]
     int seg = 0;
     while (seg + 1 < segs.n && (int) blockIdx.x >= segs.tile_begin[seg + 1]) ++seg;
@@ -53,68 +63,81 @@ __global__ void __launch_bounds__(TPB) conv111_kernel(SegTable segs, const T* __
     T acc[OB];
 #pragma unroll
     for (int o = 0; o < OB; ++o) acc[o] = 0;
+    auto mix = [&](const T v, const int i) {
+        const V* wr = reinterpret_cast<const V*>(wsm + i * OB);
+#pragma unroll
+        for (int o = 0; o < OB / VN; ++o) {
+            const V wv = wr[o];
+            const T* we = reinterpret_cast<const T*>(&wv);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) acc[o * VN + e] = fma(v, we[e], acc[o * VN + e]);
+        }
+    };
     int i = 0;
     for (; i + 8 <= n_in; i += 8) {          // eight independent loads in flight per thread
         T v[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) v[k] = in[(ll) (i + k) * ld_in + p];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const T* wr = wsm + (i + k) * OB;
-#pragma unroll
-            for (int o = 0; o < OB; ++o) acc[o] = fma(v[k], wr[o], acc[o]);
-        }
+        for (int k = 0; k < 8; ++k) mix(v[k], i + k);
     }
-    for (; i < n_in; ++i) {
-        const T v = in[(ll) i * ld_in + p];
-        const T* wr = wsm + i * OB;
-#pragma unroll
-        for (int o = 0; o < OB; ++o) acc[o] = fma(v, wr[o], acc[o]);
-    }
+    for (; i < n_in; ++i) mix(in[(ll) i * ld_in + p], i);
 #pragma unroll
     for (int o = 0; o < OB; ++o)
         if (o0 + o < n_out) out[(ll) (o0 + o) * ld_out + p] = acc[o];
 }
 
 // Weight gradient of one segment: partial[chunk][o][i] = sum over the chunk's particles of
-// gout[o][p] * in[i][p].  Block tile 32 (o) x 32 (i), 256 threads, 2x2 outputs per thread.
+// gout[o][p] * in[i][p].  Block tile 64 (o) x 64 (i), 256 threads, 4x4 outputs per thread: per particle a thread
+// reads 4 + 4 values from shared memory (two 16-byte reads for floats) for 16 multiply-adds.
 template<typename T>
 __global__ void __launch_bounds__(256) conv111_dw_partial_kernel(ll seg_begin, ll seg_end, ll chunk_len,
                                                                  const T* __restrict__ in, ll ld_in,
                                                                  const T* __restrict__ gout, ll ld_out,
                                                                  T* __restrict__ partial, int cin, int cout) {
-    __shared__ T gs[32][33];
-    __shared__ T xs[32][33];
-    const int nib = (cin + 31) / 32;
+    constexpr int TILE = 64, KC = 32;
+    // [particle][channel]: a thread's four channels are contiguous; rows padded by 4 so that the transposing stores of a
+    // warp (32 particles of one channel) spread over 8 banks instead of one
+    __shared__ __align__(16) T gs[KC][TILE + 4];
+    __shared__ __align__(16) T xs[KC][TILE + 4];
+    const int nib = (cin + TILE - 1) / TILE;
     const int ob = blockIdx.y / nib, ib = blockIdx.y % nib;
     const ll pb = seg_begin + (ll) blockIdx.x * chunk_len;
     const ll pe = min(seg_end, pb + chunk_len);
-    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;          // i pair, o pair
-    T acc[2][2] = {{0, 0}, {0, 0}};
-    for (ll p0 = pb; p0 < pe; p0 += 32) {
-        for (int e = threadIdx.x; e < 32 * 32; e += 256) {
-            const int r = e >> 5, k = e & 31;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;          // 4 input channels, 4 output channels
+    T acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0;
+    for (ll p0 = pb; p0 < pe; p0 += KC) {
+        // consecutive threads read consecutive particles of one channel row (coalesced), stored transposed
+        for (int e = threadIdx.x; e < TILE * KC; e += 256) {
+            const int r = e / KC, k = e % KC;
             const bool inr = p0 + k < pe;
-            const int o = ob * 32 + r, i = ib * 32 + r;
-            gs[r][k] = (inr && o < cout) ? gout[(ll) o * ld_out + p0 + k] : T(0);
-            xs[r][k] = (inr && i < cin) ? in[(ll) i * ld_in + p0 + k] : T(0);
+            const int o = ob * TILE + r, i = ib * TILE + r;
+            gs[k][r] = (inr && o < cout) ? gout[(ll) o * ld_out + p0 + k] : T(0);
+            xs[k][r] = (inr && i < cin) ? in[(ll) i * ld_in + p0 + k] : T(0);
         }
         __syncthreads();
 #pragma unroll 8
-        for (int k = 0; k < 32; ++k) {
-            const T g0 = gs[2 * ty][k], g1 = gs[2 * ty + 1][k];
-            const T x0 = xs[2 * tx][k], x1 = xs[2 * tx + 1][k];
-            acc[0][0] = fma(g0, x0, acc[0][0]); acc[0][1] = fma(g0, x1, acc[0][1]);
-            acc[1][0] = fma(g1, x0, acc[1][0]); acc[1][1] = fma(g1, x1, acc[1][1]);
+        for (int k = 0; k < KC; ++k) {
+            T g[4], x[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) { g[a] = gs[k][4 * ty + a]; x[a] = xs[k][4 * tx + a]; }
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = fma(g[a], x[b], acc[a][b]);
         }
         __syncthreads();
     }
     T* dst = partial + (ll) blockIdx.x * cout * cin;
 #pragma unroll
-    for (int a = 0; a < 2; ++a)
+    for (int a = 0; a < 4; ++a)
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {
-            const int o = ob * 32 + 2 * ty + a, i = ib * 32 + 2 * tx + b;
+        for (int b = 0; b < 4; ++b) {
+            const int o = ob * TILE + 4 * ty + a, i = ib * TILE + 4 * tx + b;
             if (o < cout && i < cin) dst[(ll) o * cin + i] = acc[a][b];
         }
 }
@@ -216,7 +239,9 @@ int conv111_dw(const aprnet_apr* a, int dl, int cin, int cout, int S, const T* i
         const ll len = s.end - s.begin;
         const int nchunks = (int) std::min<ll>(dw_max_chunks(cin, cout), (len + 1023) / 1024);
         const ll chunk_len = ((len + nchunks - 1) / nchunks + 31) / 32 * 32;
-        dim3 grid((unsigned) nchunks, (unsigned) (aprnet_ceil_div(cout, 32) * aprnet_ceil_div(cin, 32)));
+        // few outputs: blocks of 32 input channels (conv111_dw_small_kernel); else 64 x 64 tiles
+        const unsigned gy = cout <= 4 ? (unsigned) aprnet_ceil_div(cin, 32) : (unsigned) (aprnet_ceil_div(cout, 64) * aprnet_ceil_div(cin, 64));
+        dim3 grid((unsigned) nchunks, gy);
         { AprnetProfScope _prof("conv111_dw", st);
         if (cout <= 4) conv111_dw_small_kernel<T, 4><<<grid, 256, 0, st>>>(s.begin, s.end, chunk_len, in, ld_in, gout, ld_out, partial, cin, cout);
         else conv111_dw_partial_kernel<T><<<grid, 256, 0, st>>>(s.begin, s.end, chunk_len, in, ld_in, gout, ld_out, partial, cin, cout);

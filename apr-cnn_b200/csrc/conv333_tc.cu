@@ -710,6 +710,12 @@ static int conv333_backward_tc_rows_impl(aprnet_apr* a, int dl, int cin, int cou
     if (!gin) return APRNET_OK;          // the caller does not need the input gradient (first layer of a network)
     if ((rc = aprnet_tc_gather_conv(a, dl, 1, cin, cout, slots, grows, gpad, n, n, w, wp, gin, ld_in, st))) return rc;
     void* edge_ws = (char*) wp + aprnet_tc_weight_bytes(cout, cin, slots);
+    if (27 * n + 1 >= (1ll << 31)) {
+        // more than 79.5 M locations: the 32-bit edge ids of the edge plan run out.  The cross-level part then runs on the
+        // fp32 scatter kernel (atomic adds: correct, but the summation order is no longer fixed).
+        if (!tree_adjoint) { aprnet_set_error("the split backward form needs the edge plan, which supports up to 79.5 M locations"); return APRNET_ERR_UNSUPPORTED; }
+        return aprnet_conv333_backward_input_cross_level(a, dl, APRNET_F32, cin, cout, slots, gout, ld_out, w, gin, ld_in, gtree, ld_tree, stream);
+    }
     return aprnet_cross_level_tc(a, dl, cin, cout, slots, grows, gpad, w, gin, ld_in, gtree, ld_tree, wp, edge_ws,
                                  aprnet_edge_workspace_bytes(a, dl, cout), st, tree_adjoint);
 }

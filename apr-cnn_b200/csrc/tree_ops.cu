@@ -11,14 +11,8 @@
 namespace {
 
 typedef long long ll;
-#ifndef APRNET_TREE_TPB
-#define APRNET_TREE_TPB 256
-#endif
-#ifndef APRNET_TREE_CH
-#define APRNET_TREE_CH 8
-#endif
-constexpr int TPB = APRNET_TREE_TPB;
-constexpr int CH_PER_BLOCK = APRNET_TREE_CH;
+constexpr int TPB = 256;                 // threads (= parent nodes) per block
+constexpr int CH_PER_BLOCK = 8;          // channels a block loops over with the child slots resolved once
 
 template<typename T> struct DT;
 template<> struct DT<float> { static constexpr int id = APRNET_F32; };

@@ -21,12 +21,13 @@ class Conv333Function(Function):
     """3x3x3 stencil: the given stencils are expanded to one per level, then applied per level."""
 
     @staticmethod
-    def forward(ctx, inputs, weights, bias, aprs, level_deltas):
+    def forward(ctx, inputs, weights, bias, aprs, level_deltas, precision=None):
         num_levels = max(a.level_max() - a.level_min() + 1 for a in aprs)
         expanded = restrict_kernel333_forward(weights, num_levels)
         ctx.aprs = aprs
         ctx.num_stencils = weights.shape[0]
-        ctx.packed = get_conv_precision() == "bf16" and inputs.dtype == torch.float32
+        # arithmetic of this layer: the module's own setting, else the process-wide one
+        ctx.packed = (precision or get_conv_precision()) == "bf16" and inputs.dtype == torch.float32
         if ctx.packed:
             # tensor-core path: the backward pass works from the packed bf16 rows of the input (particles + tree
             # means) that the forward pass produced anyway; they replace the fp32 input among the saved tensors
@@ -36,7 +37,7 @@ class Conv333Function(Function):
         else:
             # the tree means computed by the forward pass are kept (1/7 of the input's size) so that the
             # backward pass does not have to fill the tree again
-            out, tree = conv333_forward_keep_tree(APRPtrVector(aprs), inputs, expanded, level_deltas)
+            out, tree = conv333_forward_keep_tree(APRPtrVector(aprs), inputs, expanded, level_deltas, "fp32")
             ctx.save_for_backward(inputs, expanded, bias, level_deltas.clone(), tree)
         if bias is not None:
             out = out + bias.view(1, -1, 1)
@@ -51,14 +52,14 @@ class Conv333Function(Function):
                                                                    bool(ctx.needs_input_grad[0]))
             grad_weights = restrict_kernel333_backward(grad_expanded, ctx.num_stencils)
             grad_bias = grad_output.sum(dim=(0, 2)) if bias is not None else None
-            return grad_input, grad_weights, grad_bias, None, None
+            return grad_input, grad_weights, grad_bias, None, None, None
         inputs, expanded, bias, level_deltas, tree = ctx.saved_tensors
         # the input gradient of a first layer (features that do not require grad) is not computed
         grad_input, grad_expanded = conv333_backward_with_tree(APRPtrVector(ctx.aprs), inputs, expanded, grad_output, level_deltas, tree,
-                                                               bool(ctx.needs_input_grad[0]))
+                                                               bool(ctx.needs_input_grad[0]), "fp32")
         grad_weights = restrict_kernel333_backward(grad_expanded, ctx.num_stencils)
         grad_bias = grad_output.sum(dim=(0, 2)) if bias is not None else None
-        return grad_input, grad_weights, grad_bias, None, None
+        return grad_input, grad_weights, grad_bias, None, None, None
 
 
 class Conv111Function(Function):
@@ -86,8 +87,14 @@ _FUNCTIONS = {(1, 1, 1): Conv111Function, (3, 3, 3): Conv333Function}
 
 
 class APRConv(nn.Module):
-    def __init__(self, in_channels, out_channels, nstencils=1, kernel_size=(3, 3, 3), bias=True):
+    """`precision` (not in the reference): arithmetic of a 3x3x3 layer on float32 tensors, "fp32" (CUDA-core kernels,
+    exact) or "bf16" (tensor cores, bf16 operands with fp32 accumulation); None follows the process-wide setting
+    (`set_conv_precision`)."""
+
+    def __init__(self, in_channels, out_channels, nstencils=1, kernel_size=(3, 3, 3), bias=True, precision=None):
         super().__init__()
+        assert precision in (None, "fp32", "bf16")
+        self.precision = precision
         kernel_size = tuple(kernel_size)
         assert kernel_size in _FUNCTIONS, \
             'aprnet.cuda.APRConv currently only supports kernels of size (1, 1, 1) and (3, 3, 3)'
@@ -112,4 +119,6 @@ class APRConv(nn.Module):
             init.uniform_(self.bias, -bound, bound)
 
     def forward(self, input_features, aprs, level_deltas):
+        if self.kernel_size == (3, 3, 3):
+            return self._function.apply(input_features, self.weight, self.bias, aprs, level_deltas, self.precision)
         return self._function.apply(input_features, self.weight, self.bias, aprs, level_deltas)

@@ -45,8 +45,8 @@ class GpuBackend:
     def fill_tree(self, aprs, x, ld):
         return self.C.fill_tree_mean_batch(self.vec(aprs), x, ld)
 
-    def conv_forward(self, aprs, x, tree, w, ld):
-        return self.C.conv333_forward_pretree(self.vec(aprs), x, tree, w, ld)
+    def conv_forward(self, aprs, x, tree, w, ld, precision=None):
+        return self.C.conv333_forward_pretree(self.vec(aprs), x, tree, w, ld, precision or "")
 
     def conv_backward(self, aprs, x, tree, kept, w, go, ld, need_grad_input):
         return self.C.conv333_backward_pretree(self.vec(aprs), x, tree, kept, w, go, ld, need_grad_input)
@@ -97,7 +97,7 @@ class Shard:
 
 class ShardedConv333Function(Function):
     @staticmethod
-    def forward(ctx, inputs, weights, bias, aprs, level_deltas, shard):
+    def forward(ctx, inputs, weights, bias, aprs, level_deltas, shard, precision=None):
         B = shard.backend
         assert len(aprs) == 1 and inputs.shape[0] == 1, "one APR (slab) per rank"
         dl = int(level_deltas[0])
@@ -106,7 +106,8 @@ class ShardedConv333Function(Function):
         inputs = inputs.contiguous()
         tree = B.fill_tree(aprs, inputs, level_deltas)
         shard.halo.forward(dl, inputs, tree)                 # halo entries of input and tree now hold their owners' values
-        out, kept = B.conv_forward(aprs, inputs, tree, expanded, level_deltas)
+        out, kept = B.conv_forward(aprs, inputs, tree, expanded, level_deltas) if precision is None else \
+            B.conv_forward(aprs, inputs, tree, expanded, level_deltas, precision)
         if bias is not None:
             out = out + bias.view(1, -1, 1)
         shard.halo.zero_halo(dl, out)
@@ -140,7 +141,7 @@ class ShardedConv333Function(Function):
             gi = None
         gw = B.restrict_backward(gwe, ctx.num_stencils)
         gb = grad_output.sum(dim=(0, 2)) if bias is not None else None
-        return gi, gw, gb, None, None, None
+        return gi, gw, gb, None, None, None, None
 
 
 class ShardedGroupNormReLUFunction(Function):
@@ -202,7 +203,7 @@ def make_ops(shard):
     class APRConv(_conv.APRConv):
         def forward(self, input_features, aprs, level_deltas):
             if self.kernel_size == (3, 3, 3):
-                return ShardedConv333Function.apply(input_features, self.weight, self.bias, aprs, level_deltas, shard)
+                return ShardedConv333Function.apply(input_features, self.weight, self.bias, aprs, level_deltas, shard, self.precision)
             return super().forward(input_features, aprs, level_deltas)
 
     class GroupNormReLU(nn.Module):

@@ -198,7 +198,9 @@ int aprnet_conv333_backward_input_cross_level(aprnet_apr* apr, int level_delta, 
                                               void* stream);
 /* Cross-level part of the input gradient without atomics: an edge-list GEMM on the tensor cores plus a
  * per-target pull (deterministic).  The edge lists of a level delta are built once and cached
- * (aprnet_edge_plan_build allocates; call it up front).  edge_ws: aprnet_edge_workspace_bytes() bytes. */
+ * (aprnet_edge_plan_build allocates; call it up front).  edge_ws: aprnet_edge_workspace_bytes() bytes.
+ * Limit: 27 * N(level_delta) < 2^31, i.e. up to 79.5 M locations (32-bit edge ids); beyond it
+ * aprnet_conv333_backward_tc(_rows) falls back to aprnet_conv333_backward_input_cross_level (atomic adds). */
 int aprnet_edge_plan_build(aprnet_apr* apr, int level_delta, void* stream);
 int64_t aprnet_edge_workspace_bytes(const aprnet_apr* apr, int level_delta, int cout);
 int aprnet_conv333_backward_input_cross_level_tc(aprnet_apr* apr, int level_delta, int cin, int cout, int num_slots,
@@ -240,7 +242,10 @@ int aprnet_conv111_backward_weights(const aprnet_apr* apr, int level_delta, int 
  * APRNET_ERR_UNSUPPORTED; calls that overlap on one GPU race on the shared array, so serialise them;
  * the array keeps the previous call's contents (the call overwrites all it reads).  The first call on
  * each device looks up the array's device address (with that device current); make that first call
- * before starting any stream capture.  The call itself performs no allocation of any kind. */
+ * before starting any stream capture, and before a host arena claims the rest of the GPU: with lazy
+ * module loading the CUDA runtime places the library image, the 4 MiB array included, on the device at
+ * that first use, which can fail with an out-of-memory error on a GPU that is already full.  Every later
+ * call allocates nothing. */
 int aprnet_conv111_backward_weights_static(const aprnet_apr* apr, int level_delta, int cin, int cout,
                                            int num_stencils, const float* input, int64_t ld_in,
                                            const float* grad_output, int64_t ld_out, float* grad_weights,

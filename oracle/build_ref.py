@@ -16,7 +16,14 @@ import sysconfig
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def build(reference="/root/reference", force=False, verbose=True):
+def reference_root():
+    """Checkout of the reference project: the environment variable APRNET_REFERENCE, else a sibling `reference`
+    directory of this repository."""
+    return os.environ.get("APRNET_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(reference=None, force=False, verbose=True):
+    reference = reference or reference_root()
     src_dir = os.path.join(reference, "pyapr", "aprnet", "src")
     if not os.path.isfile(os.path.join(src_dir, "conv.hpp")):
         raise FileNotFoundError("reference aprnet sources not found under " + src_dir)
@@ -49,7 +56,7 @@ def build(reference="/root/reference", force=False, verbose=True):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=reference_root())
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     print(build(a.reference, a.force))

@@ -158,3 +158,42 @@ def test_groupnorm_relu_gradcheck():
     x = (torch.randn(2, 4, 50, dtype=torch.float64, device=dev) + 0.3).requires_grad_(True)
     m = aprnet.GroupNormReLU(2, 4).double().to(dev)
     assert gradcheck(lambda t: m(t), (x,), eps=1e-6, atol=1e-6)
+
+
+def test_precision_is_a_per_module_option():
+    """`APRConv(precision=...)` overrides the process-wide setting for that layer only, forward and backward."""
+    import pyapr
+    from pyapr.aprnet import cuda as aprnet
+    from _pyaprwrapper.aprnet import cuda as C
+    a = H.blob_arrays()
+    apr = pyapr.apr_from_arrays(a)
+    apr.init_cuda()
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    x = torch.rand(1, 16, a.n_particles, device=dev)
+    go = torch.randn(1, 24, a.n_particles, device=dev)
+    ld = torch.zeros(1, dtype=torch.int32)
+    convs = {p: aprnet.APRConv(16, 24, nstencils=2, precision=p).to(dev) for p in (None, "fp32", "bf16")}
+    for c in convs.values():
+        c.load_state_dict(convs[None].state_dict())
+    res = {}
+    assert C.get_conv_precision() == "fp32"
+    for mode in ("fp32", "bf16"):
+        C.set_conv_precision(mode)
+        try:
+            for p, c in convs.items():
+                c.zero_grad(set_to_none=True)
+                xi = x.clone().requires_grad_(True)
+                c(xi, [apr], ld).backward(go)
+                res[(mode, p)] = (xi.grad.clone(), c.weight.grad.clone())
+        finally:
+            C.set_conv_precision("fp32")
+    same = lambda u, v: all(torch.equal(s, t) for s, t in zip(u, v))
+    # the fp32 input gradient scatters its cross-level part with atomic adds: equal up to the summation order
+    close = lambda u, v: all(float((s - t).abs().max()) <= 1e-5 * float(t.abs().max()) for s, t in zip(u, v))
+    assert close(res[("fp32", "fp32")], res[("bf16", "fp32")]) and close(res[("fp32", None)], res[("fp32", "fp32")])       # pinned to fp32
+    assert same(res[("fp32", "bf16")], res[("bf16", "bf16")]) and same(res[("bf16", None)], res[("bf16", "bf16")])       # pinned to bf16
+    assert not close(res[("fp32", "fp32")], res[("fp32", "bf16")])
+    rel = float((res[("fp32", "fp32")][1] - res[("fp32", "bf16")][1]).abs().max() / res[("fp32", "fp32")][1].abs().max())
+    assert rel <= 2e-2
+    assert C.tc_error_flag() == 0

@@ -80,7 +80,8 @@ def test_reference_unet_builds_on_these_modules():
 
     The files are loaded directly (the package __init__ also pulls in the stardist models, which need
     the absent `stardist` dependency)."""
-    base = "/root/reference/apr_models/apr_models/unet"
+    import build_ref
+    base = os.path.join(build_ref.reference_root(), "apr_models", "apr_models", "unet")
     if not os.path.isdir(base):
         pytest.skip("reference checkout not present")
     import importlib.util
