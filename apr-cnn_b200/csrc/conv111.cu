@@ -40,8 +40,11 @@ template<> struct Vec16<double> { typedef double2 type; static constexpr int N =
 
 // out[o][p] = sum_i w[slot][o][i] * in[i][p]; weight element (s, o, i) at w[s*ws + o*wo + i*wi]
 // (forward: wo = Cin, wi = 1; input gradient: roles of the channel axes swapped, wo = 1, wi = Cin_fwd).
-template<typename T, int OB, int TPB>
-__global__ void __launch_bounds__(TPB) conv111_kernel(SegTable segs, const T* __restrict__ in, ll ld_in,
+// A thread owns PPT locations (p, p + TPB, ...) and OB output channels: every 16-byte weight read from shared memory
+// feeds 4 * PPT multiply-adds.  (With one location per thread the kernel ran at 84 % of the load/store pipe and 32 % of
+// DRAM: bound by the broadcast weight reads.)
+template<typename T, int OB, int TPB, int PPT>
+__global__ void __launch_bounds__(TPB, sizeof(T) == 4 ? 2 : 1) conv111_kernel(SegTable segs, const T* __restrict__ in, ll ld_in,
                                                       const T* __restrict__ w, ll ws, ll wo, ll wi,
                                                       T* __restrict__ out, ll ld_out, int n_in, int n_out) {
     typedef typename Vec16<T>::type V;
@@ -51,7 +54,8 @@ __global__ void __launch_bounds__(TPB) conv111_kernel(SegTable segs, const T* __
     T* wsm = reinterpret_cast<T*>(smem_raw);              // [n_in][OB]
     int seg = 0;
     while (seg + 1 < segs.n && (int) blockIdx.x >= segs.tile_begin[seg + 1]) ++seg;
-    const ll p = segs.begin[seg] + (ll) (blockIdx.x - segs.tile_begin[seg]) * TPB + threadIdx.x;
+    const ll p0 = segs.begin[seg] + (ll) (blockIdx.x - segs.tile_begin[seg]) * (TPB * PPT) + threadIdx.x;
+    const ll pend = segs.end[seg];
     const int o0 = blockIdx.y * OB;
     const T* wslot = w + (ll) segs.slot[seg] * ws;
     for (int e = threadIdx.x; e < n_in * OB; e += TPB) {
@@ -59,32 +63,49 @@ __global__ void __launch_bounds__(TPB) conv111_kernel(SegTable segs, const T* __
         wsm[e] = (o0 + o < n_out) ? wslot[(ll) (o0 + o) * wo + (ll) i * wi] : T(0);
     }
     __syncthreads();
-    if (p >= segs.end[seg]) return;
-    T acc[OB];
+    if (p0 >= pend) return;
+    T acc[PPT][OB];
 #pragma unroll
-    for (int o = 0; o < OB; ++o) acc[o] = 0;
-    auto mix = [&](const T v, const int i) {
+    for (int q = 0; q < PPT; ++q)
+#pragma unroll
+        for (int o = 0; o < OB; ++o) acc[q][o] = 0;
+    constexpr int IU = PPT == 1 ? 8 : 4;     // input channels whose loads are in flight together
+    auto mix = [&](const T (&v)[PPT], const int i) {
         const V* wr = reinterpret_cast<const V*>(wsm + i * OB);
 #pragma unroll
         for (int o = 0; o < OB / VN; ++o) {
             const V wv = wr[o];
             const T* we = reinterpret_cast<const T*>(&wv);
 #pragma unroll
-            for (int e = 0; e < VN; ++e) acc[o * VN + e] = fma(v, we[e], acc[o * VN + e]);
+            for (int e = 0; e < VN; ++e)
+#pragma unroll
+                for (int q = 0; q < PPT; ++q) acc[q][o * VN + e] = fma(v[q], we[e], acc[q][o * VN + e]);
         }
     };
     int i = 0;
-    for (; i + 8 <= n_in; i += 8) {          // eight independent loads in flight per thread
-        T v[8];
+    for (; i + IU <= n_in; i += IU) {
+        T v[IU][PPT];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) v[k] = in[(ll) (i + k) * ld_in + p];
+        for (int k = 0; k < IU; ++k)
 #pragma unroll
-        for (int k = 0; k < 8; ++k) mix(v[k], i + k);
+            for (int q = 0; q < PPT; ++q) v[k][q] = (p0 + (ll) q * TPB < pend) ? in[(ll) (i + k) * ld_in + p0 + (ll) q * TPB] : T(0);
+#pragma unroll
+        for (int k = 0; k < IU; ++k) mix(v[k], i + k);
     }
-    for (; i < n_in; ++i) mix(in[(ll) i * ld_in + p], i);
+    for (; i < n_in; ++i) {
+        T v[PPT];
 #pragma unroll
-    for (int o = 0; o < OB; ++o)
-        if (o0 + o < n_out) out[(ll) (o0 + o) * ld_out + p] = acc[o];
+        for (int q = 0; q < PPT; ++q) v[q] = (p0 + (ll) q * TPB < pend) ? in[(ll) i * ld_in + p0 + (ll) q * TPB] : T(0);
+        mix(v, i);
+    }
+#pragma unroll
+    for (int q = 0; q < PPT; ++q) {
+        const ll p = p0 + (ll) q * TPB;
+        if (p >= pend) break;
+#pragma unroll
+        for (int o = 0; o < OB; ++o)
+            if (o0 + o < n_out) out[(ll) (o0 + o) * ld_out + p] = acc[q][o];
+    }
 }
 
 // Weight gradient of one segment: partial[chunk][o][i] = sum over the chunk's particles of
@@ -204,15 +225,18 @@ __global__ void reduce_partial_kernel(const T* __restrict__ partial, int nchunks
 // block partials of the weight gradient: many chunks for small filters (parallelism), fewer for large ones (workspace)
 inline int dw_max_chunks(int cin, int cout) { return (int) std::max<ll>(128, std::min<ll>(2048, (16ll << 20) / ((ll) cin * cout))); }
 
-template<typename T, int OB, int TPB>
-int conv111_launch(const SegTable& segs, int tiles, const T* in, ll ld_in, const T* w, ll ws, ll wo, ll wi, T* out, ll ld_out,
+template<typename T, int OB, int TPB, int PPT>
+int conv111_launch(const aprnet_apr* a, int dl, int S, const T* in, ll ld_in, const T* w, ll ws, ll wo, ll wi, T* out, ll ld_out,
                    int n_in, int n_out, cudaStream_t st) {
+    const SegTable segs = make_seg_table(aprnet_segments(a, dl, S, true), TPB * PPT);
+    const int tiles = segs.tile_begin[segs.n];
+    if (tiles == 0) return APRNET_OK;
     const size_t smem = (size_t) n_in * OB * sizeof(T);
     if (smem > 48 * 1024)
-        APRNET_CUDA_CHECK(cudaFuncSetAttribute(conv111_kernel<T, OB, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        APRNET_CUDA_CHECK(cudaFuncSetAttribute(conv111_kernel<T, OB, TPB, PPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     dim3 grid((unsigned) tiles, (unsigned) aprnet_ceil_div(n_out, OB));
     { AprnetProfScope _prof("conv111", st);
-    conv111_kernel<T, OB, TPB><<<grid, TPB, smem, st>>>(segs, in, ld_in, w, ws, wo, wi, out, ld_out, n_in, n_out);
+    conv111_kernel<T, OB, TPB, PPT><<<grid, TPB, smem, st>>>(segs, in, ld_in, w, ws, wo, wi, out, ld_out, n_in, n_out);
     }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
@@ -222,12 +246,11 @@ template<typename T>
 int conv111_apply(const aprnet_apr* a, int dl, int n_in, int n_out, int S, const T* in, ll ld_in, const T* w,
                   ll ws, ll wo, ll wi, T* out, ll ld_out, cudaStream_t st) {
     constexpr int TPB = 256;
-    const SegTable segs = make_seg_table(aprnet_segments(a, dl, S, true), TPB);
-    const int tiles = segs.tile_begin[segs.n];
-    if (tiles == 0) return APRNET_OK;
-    if (n_out <= 4) return conv111_launch<T, 4, TPB>(segs, tiles, in, ld_in, w, ws, wo, wi, out, ld_out, n_in, n_out, st);      // e.g. a classification head
-    if (n_out <= 16) return conv111_launch<T, 16, TPB>(segs, tiles, in, ld_in, w, ws, wo, wi, out, ld_out, n_in, n_out, st);
-    return conv111_launch<T, 32, TPB>(segs, tiles, in, ld_in, w, ws, wo, wi, out, ld_out, n_in, n_out, st);      // the input is read once per 32 outputs
+    if (n_out <= 4) return conv111_launch<T, 4, TPB, 4>(a, dl, S, in, ld_in, w, ws, wo, wi, out, ld_out, n_in, n_out, st);      // e.g. a classification head
+    if (n_out <= 16) return conv111_launch<T, 16, TPB, 2>(a, dl, S, in, ld_in, w, ws, wo, wi, out, ld_out, n_in, n_out, st);
+    // the input is read once per 32 outputs; two locations per thread (fp32) halve the shared-memory reads per multiply-add
+    if (sizeof(T) == 4) return conv111_launch<T, 32, TPB, 2>(a, dl, S, in, ld_in, w, ws, wo, wi, out, ld_out, n_in, n_out, st);
+    return conv111_launch<T, 32, TPB, 1>(a, dl, S, in, ld_in, w, ws, wo, wi, out, ld_out, n_in, n_out, st);
 }
 
 template<typename T>
@@ -296,31 +319,32 @@ __global__ void restrict333_forward_kernel(int S, ll filters, const T* __restric
 // ascending order, so the sum order is fixed.
 template<typename T>
 __global__ void restrict333_backward_kernel(int S, int L, ll filters, const T* __restrict__ src, T* __restrict__ dst) {
-    const ll f = (ll) blockIdx.x * blockDim.x + threadIdx.x;
-    if (f >= filters) return;
-    T* fine = dst + ((ll) (S - 1) * filters + f) * 27;
-    for (int zi = 0; zi < 3; ++zi) for (int xi = 0; xi < 3; ++xi) for (int yi = 0; yi < 3; ++yi) {
-        T acc = src[((ll) (S - 1) * filters + f) * 27 + (zi * 3 + xi) * 3 + yi];
-        for (int k = S; k < L; ++k) {
-            const int step = 1 << (k - (S - 1));
-            const float factor = (float) step * (float) step * (float) step;
-            const T* coarse = src + ((ll) k * filters + f) * 27;
-            for (int zo = 0; zo < 3; ++zo) {
-                const float oz = restrict_overlap(step, zi, zo);
-                if (oz <= 0) continue;
-                for (int xo = 0; xo < 3; ++xo) {
-                    const float ox = restrict_overlap(step, xi, xo);
-                    if (ox <= 0) continue;
-                    for (int yo = 0; yo < 3; ++yo) {
-                        const float oy = restrict_overlap(step, yi, yo);
-                        if (oy <= 0) continue;
-                        acc += (T) (ox * oy * oz / factor) * coarse[(zo * 3 + xo) * 3 + yo];
-                    }
+    // one thread per (filter, fine tap): 27 times the parallelism of one thread per filter, same summation order
+    const ll e = (ll) blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= filters * 27) return;
+    const ll f = e / 27;
+    const int tap = (int) (e - f * 27);
+    const int zi = tap / 9, xi = (tap / 3) % 3, yi = tap % 3;
+    T acc = src[((ll) (S - 1) * filters + f) * 27 + tap];
+    for (int k = S; k < L; ++k) {
+        const int step = 1 << (k - (S - 1));
+        const float factor = (float) step * (float) step * (float) step;
+        const T* coarse = src + ((ll) k * filters + f) * 27;
+        for (int zo = 0; zo < 3; ++zo) {
+            const float oz = restrict_overlap(step, zi, zo);
+            if (oz <= 0) continue;
+            for (int xo = 0; xo < 3; ++xo) {
+                const float ox = restrict_overlap(step, xi, xo);
+                if (ox <= 0) continue;
+                for (int yo = 0; yo < 3; ++yo) {
+                    const float oy = restrict_overlap(step, yi, yo);
+                    if (oy <= 0) continue;
+                    acc += (T) (ox * oy * oz / factor) * coarse[(zo * 3 + xo) * 3 + yo];
                 }
             }
         }
-        fine[(zi * 3 + xi) * 3 + yi] = acc;
     }
+    dst[((ll) (S - 1) * filters + f) * 27 + tap] = acc;
 }
 
 template<typename T>
@@ -328,7 +352,7 @@ int restrict333(int S, int L, ll filters, const T* src, T* dst, bool backward, c
     APRNET_CUDA_CHECK(cudaMemcpyAsync(dst, src, (size_t) S * filters * 27 * sizeof(T), cudaMemcpyDeviceToDevice, st));
     if (L > S) {
         if (backward) {
-            restrict333_backward_kernel<T><<<aprnet_ceil_div(filters, 128), 128, 0, st>>>(S, L, filters, src, dst);
+            restrict333_backward_kernel<T><<<aprnet_ceil_div(filters * 27, 128), 128, 0, st>>>(S, L, filters, src, dst);
         } else {
             dim3 grid((unsigned) aprnet_ceil_div(filters, 128), (unsigned) (L - S));
             restrict333_forward_kernel<T><<<grid, 128, 0, st>>>(S, filters, src, dst);

@@ -28,6 +28,7 @@ from . import aprnet  # noqa: E402
 from . import tree  # noqa: E402
 from . import synthetic  # noqa: E402
 from . import sharding  # noqa: E402
+from . import io  # noqa: E402
 
 
 def cuda_enabled() -> bool:

@@ -154,3 +154,34 @@ def test_gradient_allreduce_two_ranks_gloo():
     for g0, g1, m0, m1 in zip(l0, l1, a0, a1):
         want = (np.array(g0) + np.array(g1)) / 2
         assert np.allclose(m0, want) and np.allclose(m1, want)
+
+
+def test_apr_file_round_trip_and_libapr_conversion(tmp_path):
+    """write_apr / read_apr keep the access arrays bit for bit; the LibAPR-layout conversion reproduces them."""
+    import pyapr
+    from pyapr import io
+    a = H.arrays("odd2")
+    feat = np.random.RandomState(0).rand(3, a.n_particles).astype(np.float32)
+    path = str(tmp_path / "odd2.npz")
+    io.write_apr(path, a, name="odd2", particle_data=feat)
+    b, name, data = io.read_apr(path)
+    assert name == "odd2" and b.shape == a.shape and b.level_max == a.level_max and b.dims == a.dims
+    for f in ("row_ptr", "y", "tree_row_ptr", "tree_y"):
+        assert np.array_equal(getattr(a, f), getattr(b, f))
+    assert np.array_equal(data, feat)
+    apr = pyapr.apr_from_arrays(b)
+    assert apr.total_number_particles() == a.n_particles
+    # LibAPR layout: rows of ALL levels from 0 (empty below level_min), row ends instead of CSR pointers
+    rows_below = sum(a.dims[l][0] * a.dims[l][1] for l in range(0, a.level_min))
+    level_xz, off = [], 0
+    for l in range(a.level_max + 1):
+        level_xz.append(off)
+        off += a.dims[l][0] * a.dims[l][1]
+    xz_end = np.concatenate([np.zeros(rows_below, dtype=np.int64), a.row_ptr[1:]])
+    c = io.from_libapr_arrays(a.shape, a.level_min, a.level_max, level_xz, xz_end, a.y, level_xz, a.tree_row_ptr[1:], a.tree_y)
+    for f in ("row_ptr", "y", "tree_row_ptr", "tree_y"):
+        assert np.array_equal(getattr(a, f), getattr(c, f))
+    bad = io.AprArrays(shape=a.shape, level_max=a.level_max, level_min=a.level_min, dims=a.dims, row_ptr=a.row_ptr[:-1], y=a.y,
+                       tree_row_ptr=a.tree_row_ptr, tree_y=a.tree_y)
+    with pytest.raises(ValueError):
+        io.check_arrays(bad)
