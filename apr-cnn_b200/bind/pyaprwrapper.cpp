@@ -983,7 +983,7 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
         check(aprnet_tc_selftest_wait_timeout(max_polls, (void*) at::cuda::getCurrentCUDAStream().stream()), "tc_selftest_wait_timeout");
     }, "max_polls"_a = 1000, "Test hook: a kernel whose bounded wait runs out and raises the tensor-core error flag");
     cuda.def("tc_set_option", [](const std::string& name, int value) { check(aprnet_tc_set_option(name.c_str(), value), "tc_set_option"); },
-             "name"_a, "value"_a, "Switches of the tensor-core kernels ('tma_gather': 1 = source rows by TMA tile::gather4 instead of cp.async)");
+             "name"_a, "value"_a, "Measurement switches of the tensor-core gather kernel ('taps', 'wps', 'ks'; 0 = automatic)");
     cuda.def("measure_fp32_fma_tflops", [](int repeats) {
         double v = 0.0;
         check(aprnet_measure_fp32_fma_tflops(repeats, &v, (void*) at::cuda::getCurrentCUDAStream().stream()), "measure_fp32_fma_tflops");

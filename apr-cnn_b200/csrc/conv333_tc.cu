@@ -24,7 +24,6 @@
 #include "apr_device.cuh"
 #include "tc_ptx.cuh"
 #include <cuda_bf16.h>
-#include <cuda.h>
 #include <algorithm>
 #include <cstring>
 
@@ -136,24 +135,27 @@ struct TcParams {
     // added to out[:, t] for t < out_split and to out2[:, t - out_split] otherwise
     const int32_t* out_map; ll out_split;
     float* out2; ll ld_out2;
-    int use_tma;                           // source rows are fetched by the TMA unit (tile::gather4) instead of cp.async
 };
 
 // ---- warp-specialised gather kernel ---------------------------------------------------------------
-// One persistent block per SM, 13 warps (forward pass and both parts of the input gradient):
-//   warps 0-7   producers.  A stage (one tap, KS channels, 128 rows) belongs to ONE warp: warp w fills the
-//               stages w, w + 8, w + 16 ... of the block's stage sequence, so eight stages are being issued
-//               at once and the per-stage bookkeeping (slot wait, weight copy, barrier arrival) is paid
-//               once per 4 * KS / 8 copy instructions.  Lane 0 streams the stage's weight tile with one bulk
-//               copy (byte-counting arrival); every lane attaches an asynchronous arrival to the stage's
-//               barrier (cp.async.mbarrier.arrive.noinc), so the stage is handed to the MMA warp the moment
-//               its copies land.  Producers only block on a ring slot the tensor core still reads.
-//               With use_tma the 128 row pieces of a stage are 32 tile::gather4 copies (one per lane, four
-//               rows each) through a tensor map of the packed rows whose swizzle mode equals the operand's:
-//               the TMA unit writes the swizzled layout itself and the copies bypass the L1 data pipe;
-//   warp 8      one thread issues the tcgen05.mma of each stage, in stage order, as soon as its barrier
-//               completes, and commits the stage's "slot free" barrier; accumulators rotate through
-//               NACC TMEM buffers so that later tiles start while earlier ones are read back;
+// One persistent block per SM, 13 warps (forward pass and both parts of the input gradient).  The unit of
+// hand-over between the roles is a STAGE: TAPS consecutive taps x KS channels x 128 rows of the A operand plus the
+// TAPS weight tiles that meet them.  Consecutive taps differ in dy only (tap = (dz * 3 + dx) * 3 + dy), so with
+// TAPS = 3 a stage holds the three y-neighbours of one neighbour row.  A dependent mbarrier wait costs the waiting
+// thread about 200 cycles and a tcgen05.commit about 50 whatever the stage holds (measured), so the MMA thread, which
+// consumes the stages in order, wants few and large stages; a producer warp, on the other hand, sustains only one
+// 512-byte copy instruction per ~100 cycles, so all eight must copy all the time.
+//   warps 0-7   producers in groups of WPS warps.  A stage belongs to ONE group (group q fills the stages q,
+//               q + NG, q + 2 NG ... of the block's stage sequence, NG = 8 / WPS groups work on NG stages at once);
+//               inside the group warp s copies rows [s * 128 / WPS, (s + 1) * 128 / WPS) of every tap of the stage
+//               with 16-byte cp.async copies straight into the hardware-swizzled K-major operand layout.  Every
+//               lane attaches an asynchronous arrival to the stage's barrier (cp.async.mbarrier.arrive.noinc), so the
+//               stage is handed to the MMA thread the moment its copies land and no producer ever waits for its own
+//               copies; the first lane of the group streams the stage's weight tiles with bulk copies
+//               (byte-counting arrival).  Producers only block on a ring slot the tensor core still reads;
+//   warp 8      one thread issues the TAPS * KS / 16 tcgen05.mma of each stage back to back, in stage order, as soon
+//               as the stage's barrier completes, and commits the stage's "slot free" barrier; accumulators rotate
+//               through NACC TMEM buffers so that later tiles start while earlier ones are read back;
 //   warps 9-12  epilogue: TMEM -> registers -> global for tile i; the neighbour-table entries of tile
 //               i + NIDX are requested into registers before the wait for tile i and decoded into the
 //               source-row buffer tile i has released afterwards, so their DRAM latency is never exposed.
@@ -178,30 +180,34 @@ __device__ __forceinline__ TileInfo tile_info(const TcParams& P, int work) {
     return t;
 }
 
-template<int NT, int KS, int NACC>
-__global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcParams P, const int stages, const __grid_constant__ CUtensorMap row_map) {
+template<int NT, int KS, int TAPS, int WPS, int NACC>
+__global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcParams P, const int stages) {
     // A operand: K-major with the hardware swizzle whose width equals the row piece of one stage (KS
     // channels = 32, 64 or 128 bytes).  A gathered row piece is then contiguous in shared memory as it is
     // in global memory (its 16-byte chunks permuted inside the piece), so the lanes that copy one piece
     // write one contiguous block; with the unswizzled layout every 16-byte chunk of a row goes to a
     // different plane and each 32-byte sector costs its own pass of the shared-memory write pipe.
     constexpr int NIDX = WS_NIDX;
+    constexpr int NG = WS_NPROD / WPS;                       // producer groups = stages in issue at once
     constexpr int CH = KS / 8;                               // 16-byte chunks per gathered row piece
     constexpr int RW = 32 / CH;                              // rows covered by one copy instruction of a warp
-    constexpr int NI = TILE_M / RW;                          // copy instructions per stage
+    constexpr int WROWS = TILE_M / WPS;                      // rows of a tap that one warp of the group copies
+    constexpr int NI = WROWS / RW;                           // its copy instructions per tap
     constexpr int ROW_BYTES = KS * 2;
     constexpr uint32_t A_LAYOUT = KS == 64 ? 2u : (KS == 32 ? 4u : 6u);     // SWIZZLE_128B / 64B / 32B
-    constexpr int A_BYTES = TILE_M * ROW_BYTES;
-    constexpr int B_BYTES = NT * KS * 2;
-    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int A_TAP = TILE_M * ROW_BYTES;
+    constexpr int B_TAP = NT * KS * 2;
+    constexpr int STAGE_BYTES = TAPS * (A_TAP + B_TAP);
+    constexpr int NTG = (27 + TAPS - 1) / TAPS;              // tap groups per tile
     constexpr uint32_t IDESC = make_idesc(NT, false, false);
+    static_assert(WS_NPROD % WPS == 0 && NI >= 1 && WROWS % RW == 0, "a producer warp copies whole instructions");
     extern __shared__ __align__(128) unsigned char smem_raw[];
     // swizzle atoms (8 rows) must start on a multiple of their size: align the ring to 1024 bytes
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char* stage_base = smem;
     int32_t* idx_s = reinterpret_cast<int32_t*>(smem + (size_t) stages * STAGE_BYTES);      // NIDX x [27][128] source rows
     uint64_t* bars = reinterpret_cast<uint64_t*>(idx_s + NIDX * 27 * TILE_M);
-    uint64_t* full = bars;                          // [stages]  copies of the stage landed (32 lanes + weight bytes)
+    uint64_t* full = bars;                          // [stages]  copies of the stage landed (WPS x 32 lanes + weight bytes)
     uint64_t* empty = bars + WS_MAX_STAGES;         // [stages]  MMAs that read the stage completed
     uint64_t* tmem_full = empty + WS_MAX_STAGES;    // [NACC]    accumulator complete
     uint64_t* tmem_empty = tmem_full + WS_MAX_ACC;  // [NACC]    accumulator read back (one arrival per epilogue warp)
@@ -211,13 +217,13 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kchunks = P.kpad / KS;
-    const int steps_per_tile = 27 * kchunks;
+    const int steps_per_tile = NTG * kchunks;
     const int total_tiles = P.segs.tile_begin[P.segs.n] * P.n_tiles;
     const int my_tiles = (int) blockIdx.x < total_tiles ? (total_tiles - (int) blockIdx.x + (int) gridDim.x - 1) / (int) gridDim.x : 0;
-    const int nprod = min(WS_NPROD, stages);
+    const int ngroups = min(NG, stages);            // groups that take part (every group's first stage has its own slot)
 
     if (tid == 0) {
-        for (int i = 0; i < stages; ++i) { mbar_init(smem_u32(full + i), P.use_tma ? 1 : 32 + 1); mbar_init(smem_u32(empty + i), 1); }
+        for (int i = 0; i < stages; ++i) { mbar_init(smem_u32(full + i), WPS * 32 + 1); mbar_init(smem_u32(empty + i), 1); }
         for (int i = 0; i < NACC; ++i) { mbar_init(smem_u32(tmem_full + i), 1); mbar_init(smem_u32(tmem_empty + i), 4); }
         for (int i = 0; i < NIDX; ++i) mbar_init(smem_u32(idx_full + i), 4);
         *abort_flag = 0;
@@ -233,11 +239,12 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
 
     if (warp < WS_NPROD) {
         // ---------------- producers ----------------
-        if (warp < nprod) {
-            const int j = lane % CH, r0 = lane / CH;
+        const int grp = warp / WPS, sub = warp % WPS;
+        if (grp < ngroups) {
+            const int j = lane % CH, r0 = sub * WROWS + lane / CH;
             const uint32_t total_stages = (uint32_t) my_tiles * (uint32_t) steps_per_tile;
-            uint32_t g = warp, slot = warp, use = 0;       // nprod <= stages: the first stage of every warp has its own slot
-            int it = 0, step = warp, cur_it = -1;
+            uint32_t g = grp, slot = grp, use = 0;
+            int it = 0, step = grp, cur_it = -1;
             const int32_t* idx = idx_s;
             const unsigned char* wsrc = nullptr;
             const ll w_tap_stride = (ll) P.n_tiles * P.kpad * NT * 2;
@@ -246,40 +253,39 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
                 if (it != cur_it) {
                     cur_it = it;
                     if (!mbar_wait_warp(smem_u32(idx_full + it % NIDX), (it / NIDX) & 1, abort_flag)) { failed = true; break; }
-                    idx = idx_s + (it % NIDX) * 27 * TILE_M;
-                    if (lane == 0) {      // packed weights of one (slot, tap, n tile) are [k chunk][n][8]; a stage takes KS / 8 chunks
+                    idx = idx_s + (it % NIDX) * 27 * TILE_M + r0;
+                    if (sub == 0 && lane == 0) {      // packed weights of one (slot, tap, n tile) are [k chunk][n][8]; a stage takes KS / 8 chunks of TAPS taps
                         const TileInfo ti = tile_info(P, blockIdx.x + it * gridDim.x);
                         wsrc = reinterpret_cast<const unsigned char*>(P.wp + ((ll) ti.slot * 27 * P.n_tiles + ti.ntile) * ((ll) P.kpad * NT));
                     }
                 }
-                const int tap = step / kchunks, kc = step - tap * kchunks;
+                const int tg = step / kchunks, kc = step - tg * kchunks;
+                const int t0 = tg * TAPS;
                 if (use > 0 && !mbar_wait_warp(smem_u32(empty + slot), (use - 1) & 1, abort_flag)) { failed = true; break; }
                 unsigned char* a_s = stage_base + (size_t) slot * STAGE_BYTES;
-                if (lane == 0) {
-                    mbar_expect_tx(smem_u32(full + slot), P.use_tma ? A_BYTES + B_BYTES : B_BYTES);
-                    bulk_copy_g2s(smem_u32(a_s + A_BYTES), wsrc + (ll) tap * w_tap_stride + (ll) kc * KS * NT * 2, B_BYTES, smem_u32(full + slot));
+                if (sub == 0 && lane == 0) {
+                    const int nt = min(TAPS, 27 - t0);
+                    mbar_expect_tx(smem_u32(full + slot), nt * B_TAP);
+                    for (int t = 0; t < nt; ++t)
+                        bulk_copy_g2s(smem_u32(a_s + TAPS * A_TAP + t * B_TAP), wsrc + (ll) (t0 + t) * w_tap_stride + (ll) kc * KS * NT * 2,
+                                      B_TAP, smem_u32(full + slot));
                     bulk_issued = true;
                 }
-                if (P.use_tma) {
-                    // lane l fetches rows 4l..4l+3; the bytes count against the arrival announced above (an
-                    // early completion only drives the byte count negative until lane 0's announcement)
-                    const int4 r = *reinterpret_cast<const int4*>(idx + tap * TILE_M + 4 * lane);
-                    tma_gather4(smem_u32(a_s + 4 * lane * ROW_BYTES), &row_map, kc * KS, r.x, r.y, r.z, r.w, smem_u32(full + slot));
-                    bulk_issued = true;
-                    g += nprod; step += nprod; slot += nprod;
-                    if (slot >= (uint32_t) stages) { slot -= stages; ++use; }
-                    continue;
-                }
-                const int32_t* idx_t = idx + tap * TILE_M + r0;
                 const __nv_bfloat16* src0 = P.rows + kc * KS + j * 8;
 #pragma unroll
-                for (int i = 0; i < NI; ++i) {
-                    const int row = i * RW + r0;
-                    cp_async16(smem_u32(a_s + row * ROW_BYTES + (swizzled_chunk<KS>(row, j) << 4)), src0 + (ll) idx_t[i * RW] * P.kpad);
+                for (int t = 0; t < TAPS; ++t) {
+                    if (t0 + t < 27) {
+                        const int32_t* idx_t = idx + (t0 + t) * TILE_M;
+#pragma unroll
+                        for (int i = 0; i < NI; ++i) {
+                            const int row = r0 + i * RW;
+                            cp_async16(smem_u32(a_s + t * A_TAP + row * ROW_BYTES + (swizzled_chunk<KS>(row, j) << 4)), src0 + (ll) idx_t[i * RW] * P.kpad);
+                        }
+                    }
                 }
                 // the stage's barrier receives this thread's arrival when the copies above have landed
                 cp_async_arrive_noinc(smem_u32(full + slot));
-                g += nprod; step += nprod; slot += nprod;
+                g += ngroups; step += ngroups; slot += ngroups;
                 if (slot >= (uint32_t) stages) { slot -= stages; ++use; }
             }
             cp_async_commit();
@@ -293,20 +299,28 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
                 const uint32_t acc = (uint32_t) it % NACC, acc_use = (uint32_t) it / NACC;
                 if (acc_use > 0 && !mbar_wait(smem_u32(tmem_empty + acc), (acc_use - 1) & 1, abort_flag)) { failed = true; break; }
                 tc_fence_after();
+                const uint32_t d_addr = tmem_d + acc * NT;
+                int t0 = 0, kc = 0;
                 for (int step = 0; step < steps_per_tile; ++step) {
                     if (!mbar_wait(smem_u32(full + slot), use & 1, abort_flag)) { failed = true; break; }
-                    if (!P.use_tma) fence_proxy_async();          // generic-proxy writes of the cp.async copies -> tensor-core (async proxy) reads
+                    fence_proxy_async();          // generic-proxy writes of the cp.async copies -> tensor-core (async proxy) reads
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(stage_base + (size_t) slot * STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + A_BYTES;
-                    // descriptors of the stage's first MMA; the others add the encoded byte offset of their K slice
+                    // descriptors of the stage's first MMA; the others add the encoded byte offset of their operand
                     const uint64_t da0 = make_desc(a_addr, 16, 8 * ROW_BYTES, A_LAYOUT);
-                    const uint64_t db0 = make_desc(b_addr, NT * 16, 128, 0);
+                    const uint64_t db0 = make_desc(a_addr + TAPS * A_TAP, NT * 16, 128, 0);
 #pragma unroll
-                    for (int k = 0; k < KS / 16; ++k)
-                        umma_bf16(tmem_d + acc * NT, da0 + (uint64_t) (k * 2), db0 + (uint64_t) (k * 2 * NT), IDESC, (step > 0 || k > 0) ? 1u : 0u);
+                    for (int t = 0; t < TAPS; ++t) {
+                        if (t0 + t < 27) {
+#pragma unroll
+                            for (int k = 0; k < KS / 16; ++k)
+                                umma_bf16(d_addr, da0 + (uint64_t) ((t * A_TAP + k * 32) >> 4), db0 + (uint64_t) ((t * B_TAP + k * 2 * (NT * 16)) >> 4),
+                                          IDESC, (step > 0 || t > 0 || k > 0) ? 1u : 0u);
+                        }
+                    }
                     umma_commit(smem_u32(empty + slot));
                     if (++slot == (uint32_t) stages) { slot = 0; ++use; }
+                    if (++kc == kchunks) { kc = 0; t0 += TAPS; }
                 }
                 if (!failed) umma_commit(smem_u32(tmem_full + acc));
             }
@@ -418,82 +432,88 @@ inline int pick_nt(int n) { return n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 12
 
 struct TcGeom { int kpad, ks, nt, n_tiles; size_t rows_bytes, w_bytes; };
 
+int g_ks_override = 0;       // aprnet_tc_set_option("ks", n): channels per stage, measurement switch
+
 TcGeom tc_geometry(ll rows, int k_dim, int n_dim, int slots) {
     TcGeom g;
     g.kpad = pad_to(k_dim, 16);
     g.nt = pick_nt(n_dim);
     g.ks = (g.kpad % 64 == 0 && g.nt <= 128) ? 64 : ((g.kpad % 32 == 0) ? 32 : 16);
+    if (g_ks_override > 0 && g.kpad % g_ks_override == 0 && (g_ks_override < 64 || g.nt <= 128)) g.ks = g_ks_override;
     g.n_tiles = (n_dim + g.nt - 1) / g.nt;
     g.rows_bytes = ((size_t) rows * g.kpad * 2 + 255) / 256 * 256;
     g.w_bytes = ((size_t) slots * 27 * g.n_tiles * g.kpad * g.nt * 2 + 255) / 256 * 256;
     return g;
 }
 
-// Tensor map of the packed rows [n_rows][kpad] (bf16) with a box of one row piece (ks channels) and the
-// swizzle mode whose span equals the piece: tile::gather4 copies four such pieces per instruction.
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// Stage geometry per tile shape: (taps per stage, producer warps per stage).  The ring needs one slot per producer
+// group plus one for the tensor core; stages are as large as that allows, because the MMA thread pays a fixed
+// ~250 cycles (dependent barrier wait + commit) per stage.
+int g_taps_override = 0, g_wps_override = 0;      // aprnet_tc_set_option("taps" / "wps", n): measurement switches
 
-int make_row_map(CUtensorMap* map, const void* rows, ll n_rows, int kpad, int ks) {
-    static EncodeTiledFn encode = nullptr;
-    if (!encode) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
-            cudaGetLastError();
-            return APRNET_ERR_UNSUPPORTED;
-        }
-        encode = reinterpret_cast<EncodeTiledFn>(fn);
-    }
-    if ((reinterpret_cast<uintptr_t>(rows) & 15) || n_rows <= 0 || n_rows >= (1ll << 31)) return APRNET_ERR_UNSUPPORTED;
-    const cuuint64_t dims[2] = {(cuuint64_t) kpad, (cuuint64_t) n_rows};
-    const cuuint64_t strides[1] = {(cuuint64_t) kpad * 2};
-    const cuuint32_t box[2] = {(cuuint32_t) ks, 1};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUtensorMapSwizzle sw = ks == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : (ks == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(rows), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? APRNET_OK : APRNET_ERR_UNSUPPORTED;
+constexpr size_t WS_FIXED = (size_t) WS_NIDX * 27 * TILE_M * 4 + (2 * WS_MAX_STAGES + 3 * WS_MAX_ACC) * 8 + 16 + 1024;      // + alignment slack
+constexpr size_t WS_SMEM = 227 * 1024 - 1024;
+
+inline int ws_stages(int nt, int ks, int taps) {
+    const size_t stage = (size_t) taps * ((size_t) TILE_M * ks * 2 + (size_t) nt * ks * 2);
+    return (int) std::min<size_t>(WS_MAX_STAGES, (WS_SMEM - WS_FIXED) / stage);
 }
 
-int g_tma_gather = 0;      // aprnet_tc_set_option("tma_gather", 1): source rows by TMA tile::gather4 instead of cp.async
+// (output tile width, channels per stage, taps per stage, warps per stage) combinations that are compiled
+#define TC_VARIANTS(X) \
+    X(32, 16, 1, 1) X(32, 16, 3, 1) X(32, 16, 9, 2) X(32, 32, 1, 1) X(32, 32, 3, 1) X(32, 32, 3, 2) X(32, 32, 9, 4) \
+    X(32, 64, 1, 1) X(32, 64, 3, 2) X(32, 64, 3, 4) \
+    X(64, 16, 1, 1) X(64, 16, 3, 1) X(64, 16, 9, 2) X(64, 32, 1, 1) X(64, 32, 3, 2) X(64, 64, 1, 1) X(64, 64, 2, 2) X(64, 64, 2, 4) X(64, 64, 3, 4) \
+    X(128, 16, 1, 1) X(128, 16, 3, 2) X(128, 32, 1, 1) X(128, 32, 2, 2) X(128, 32, 3, 4) X(128, 64, 1, 1) X(128, 64, 1, 2) X(128, 64, 2, 4) \
+    X(256, 16, 1, 1) X(256, 16, 3, 2) X(256, 32, 1, 1) X(256, 32, 2, 2) X(256, 32, 2, 4)
 
-inline int tma_gather_enabled() { return g_tma_gather; }
+inline bool tc_variant_ok(int nt, int ks, int taps, int wps) {
+    bool compiled = false;
+#define X(NT_, KS_, TAPS_, WPS_) if (nt == NT_ && ks == KS_ && taps == TAPS_ && wps == WPS_) compiled = true;
+    TC_VARIANTS(X)
+#undef X
+    return compiled && ws_stages(nt, ks, taps) >= WS_NPROD / wps + 1;
+}
 
-template<int NT, int KS>
-int launch_tc_ws(TcParams P, int total_tiles, cudaStream_t st, const char* pname) {
-    constexpr size_t STAGE = (size_t) TILE_M * KS * 2 + (size_t) NT * KS * 2;
-    constexpr size_t FIXED = (size_t) WS_NIDX * 27 * TILE_M * 4 + (2 * WS_MAX_STAGES + 3 * WS_MAX_ACC) * 8 + 16 + 1024;      // + alignment slack
+// default choice: the compiled variant with the most taps per stage whose ring holds all producer groups plus one
+// slot; among equals the one with the fewest warps per stage (more stages in issue at once)
+inline void pick_stage_shape(int nt, int ks, int* taps, int* wps) {
+    if (g_taps_override > 0 && g_wps_override > 0 && tc_variant_ok(nt, ks, g_taps_override, g_wps_override)) { *taps = g_taps_override; *wps = g_wps_override; return; }
+    *taps = 1; *wps = 1;
+    static const int tcand[4] = {9, 3, 2, 1}, wcand[3] = {1, 2, 4};
+    for (int t : tcand)
+        for (int w : wcand)
+            if (tc_variant_ok(nt, ks, t, w)) { *taps = t; *wps = w; return; }
+}
+
+template<int NT, int KS, int TAPS, int WPS>
+int launch_tc_ws(const TcParams& P, int total_tiles, cudaStream_t st, const char* pname) {
+    constexpr size_t STAGE = (size_t) TAPS * ((size_t) TILE_M * KS * 2 + (size_t) NT * KS * 2);
     constexpr int NACC = NT <= 128 ? 4 : 2;          // accumulators in flight: the SM's 512 TMEM columns, at most 4
-    auto kern = conv333_tc_ws_kernel<NT, KS, NACC>;
+    auto kern = conv333_tc_ws_kernel<NT, KS, TAPS, WPS, NACC>;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     // one block per SM with all of its shared memory (227 KB, 1 KB reserved) as the stage ring
-    int stages = (int) std::min<size_t>(WS_MAX_STAGES, (227 * 1024 - 1024 - FIXED) / STAGE);
-    if (stages < 2) { aprnet_set_error("conv333 tensor-core path: tile nt=%d ks=%d does not fit shared memory", NT, KS); return APRNET_ERR_UNSUPPORTED; }
-    const size_t smem = (size_t) stages * STAGE + FIXED;
+    const int stages = ws_stages(NT, KS, TAPS);
+    if (stages < 2) { aprnet_set_error("conv333 tensor-core path: tile nt=%d ks=%d taps=%d does not fit shared memory", NT, KS, TAPS); return APRNET_ERR_UNSUPPORTED; }
+    const size_t smem = (size_t) stages * STAGE + WS_FIXED;
     APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     const int grid = std::min(total_tiles, sms);
-    CUtensorMap row_map;
-    memset(&row_map, 0, sizeof(row_map));
-    // the map ends before the zero row: coordinate zero_row is then out of bounds and the TMA unit fills
-    // the piece with zeros without touching memory (one hot row would serialise on its L2 slice)
-    if (P.use_tma && make_row_map(&row_map, P.rows, P.zero_row, P.kpad, KS) != APRNET_OK) P.use_tma = 0;
     { AprnetProfScope _prof(pname, st);
-    kern<<<grid, WS_THREADS, smem, st>>>(P, stages, row_map);
+    kern<<<grid, WS_THREADS, smem, st>>>(P, stages);
     }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
 }
 
 int dispatch_tc(const TcParams& P, const TcGeom& g, int total_tiles, cudaStream_t st, const char* pname) {
-#define TC_CASE(NT_, KS_) if (g.nt == NT_ && g.ks == KS_) return launch_tc_ws<NT_, KS_>(P, total_tiles, st, pname);
-    TC_CASE(32, 16) TC_CASE(32, 32) TC_CASE(32, 64) TC_CASE(64, 16) TC_CASE(64, 32) TC_CASE(64, 64)
-    TC_CASE(128, 16) TC_CASE(128, 32) TC_CASE(128, 64) TC_CASE(256, 16) TC_CASE(256, 32)
-#undef TC_CASE
-    aprnet_set_error("conv333 tensor-core path: unsupported tile geometry nt=%d ks=%d", g.nt, g.ks);
+    int taps = 1, wps = 1;
+    pick_stage_shape(g.nt, g.ks, &taps, &wps);
+#define X(NT_, KS_, TAPS_, WPS_) if (g.nt == NT_ && g.ks == KS_ && taps == TAPS_ && wps == WPS_) return launch_tc_ws<NT_, KS_, TAPS_, WPS_>(P, total_tiles, st, pname);
+    TC_VARIANTS(X)
+#undef X
+    aprnet_set_error("conv333 tensor-core path: unsupported tile geometry nt=%d ks=%d taps=%d wps=%d", g.nt, g.ks, taps, wps);
     return APRNET_ERR_UNSUPPORTED;
 }
 
@@ -539,7 +559,6 @@ int aprnet_tc_gather_conv(aprnet_apr* a, int dl, int backward, int cin, int cout
     P.wp = wp; P.out = out; P.ld_out = ld_out; P.n_dim = n_dim; P.n_tiles = g.n_tiles; P.same_level_only = backward;
     P.error_flag = g_error_flag_dev;
     P.out_map = nullptr; P.out_split = 0; P.out2 = nullptr; P.ld_out2 = 0;
-    P.use_tma = tma_gather_enabled();
 
     const int total = P.segs.tile_begin[P.segs.n] * g.n_tiles;
     if (total == 0) return APRNET_OK;
@@ -626,7 +645,13 @@ extern "C" void aprnet_tc_error_reset(void) { if (g_error_flag_host) *g_error_fl
 
 extern "C" int aprnet_tc_set_option(const char* name, int value) {
     APRNET_ARG_CHECK(name, "null option name");
-    if (!strcmp(name, "tma_gather")) { g_tma_gather = value != 0; return APRNET_OK; }
+    if (!strcmp(name, "taps")) { g_taps_override = value; return APRNET_OK; }
+    if (!strcmp(name, "wps")) { g_wps_override = value; return APRNET_OK; }
+    if (!strcmp(name, "ks")) {
+        APRNET_ARG_CHECK(value == 0 || value == 16 || value == 32 || value == 64, "channels per stage must be 0 (automatic), 16, 32 or 64");
+        g_ks_override = value;
+        return APRNET_OK;
+    }
     aprnet_set_error("aprnet_tc_set_option: unknown option '%s'", name);
     return APRNET_ERR_ARG;
 }

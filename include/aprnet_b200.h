@@ -214,9 +214,9 @@ void aprnet_tc_error_reset(void);
 /* Test hook for the error path: launches one small kernel whose bounded wait (max_polls polls) is on a barrier
  * that nothing arrives at; the wait runs out, the kernel raises the flag above and returns (nothing hangs). */
 int aprnet_tc_selftest_wait_timeout(int max_polls, void* stream);
-/* Switches of the tensor-core kernels.  "tma_gather": 1 makes the forward and same-level input-gradient
- * kernels fetch their source rows with TMA tile::gather4 copies through a tensor map of the packed rows
- * instead of 16-byte cp.async copies (same results; default 0). */
+/* Measurement switches of the tensor-core gather kernel (0 = automatic): "taps" = taps of the 27 per shared-memory
+ * stage, "wps" = producer warps that fill one stage together (both must be set, and the pair must be a compiled
+ * shape whose ring fits shared memory, else the automatic choice stays), "ks" = channels per stage (16, 32, 64). */
 int aprnet_tc_set_option(const char* name, int value);
 
 /* ---- 1x1x1 convolution -----------------------------------------------------------------------

@@ -67,35 +67,35 @@ def test_conv333_tensor_core_path(name, cin, cout, nst, oracle, bf16_mode):
             assert H.rel_err(H.t2n(gw), gw_ref) <= tol_out, (name, dl, exact_inputs)
 
 
-def test_conv333_tma_gather_variant(oracle, bf16_mode):
-    """The opt-in TMA (tile::gather4) source-row path gives the same parity as the default cp.async path."""
+@pytest.mark.parametrize("taps,wps", [(1, 1), (3, 1), (3, 2), (3, 4), (2, 4), (9, 4)])
+def test_conv333_stage_shape_variants(taps, wps, oracle, bf16_mode):
+    """Every compiled stage shape of the gather kernel (taps per stage, producer warps per stage) gives the same
+    parity; shapes that do not exist for a tile geometry fall back to the automatic choice."""
     import pyapr
     from _pyaprwrapper.data_containers import APRPtrVector
     C = bf16_mode
     dev = torch.device("cuda:0")
-    C.tc_set_option("tma_gather", 1)
+    a = H.blob_arrays((48, 64, 64), 8, 5)
+    apr = pyapr.apr_from_arrays(a)
+    apr.init_cuda()
+    o = oracle.OracleAPR(a)
+    L = a.level_max - a.level_min + 1
+    rng = np.random.RandomState(5)
+    C.tc_set_option("taps", taps); C.tc_set_option("wps", wps)
     try:
-        for name in ("blob", "odd"):
-            a = H.arrays(name) if name in H.APR_CASES else H.blob_arrays()
-            apr = pyapr.apr_from_arrays(a)
-            apr.init_cuda()
-            o = oracle.OracleAPR(a)
-            L = a.level_max - a.level_min + 1
-            rng = np.random.RandomState(5)
-            for cin, cout in [(32, 32), (64, 48), (16, 136), (72, 260)]:
-                for dl in range(0, min(H.max_dl(a), 1) + 1):
-                    n = o.number_parts(dl)
-                    x = bf16_round(rng.rand(cin, n)); w = bf16_round(rng.randn(L, cout, cin, 3, 3, 3) / np.sqrt(27 * cin)); go = bf16_round(rng.randn(cout, n))
-                    ld = torch.full((1,), dl, dtype=torch.int32)
-                    xt = torch.from_numpy(x).to(dev)[None].contiguous()
-                    wt = torch.from_numpy(w).to(dev)
-                    got = torch.from_numpy(go).to(dev)[None].contiguous()
-                    out = C.conv333_forward(APRPtrVector([apr]), xt, wt, ld)
-                    gi, gw = C.conv333_backward(APRPtrVector([apr]), xt, wt, got, ld)
-                    want = o.conv333_forward(x.astype(np.float64), w.astype(np.float64), dl)
-                    gi_ref, gw_ref = o.conv333_backward(x.astype(np.float64), w.astype(np.float64), go.astype(np.float64), dl)
-                    assert H.rel_err(H.t2n(out[0]), want) <= 5e-3, (name, cin, cout, dl)
-                    assert H.rel_err(H.t2n(gi[0]), gi_ref) <= 5e-3, (name, cin, cout, dl)
-                    assert H.rel_err(H.t2n(gw), gw_ref) <= 5e-3, (name, cin, cout, dl)
+        for cin, cout, dl in [(32, 32, 0), (64, 64, 0), (64, 32, 1), (16, 48, 0), (128, 130, 1)]:
+            n = o.number_parts(dl)
+            x = bf16_round(rng.rand(cin, n)); w = bf16_round(rng.randn(L, cout, cin, 3, 3, 3) / np.sqrt(27 * cin)); go = bf16_round(rng.randn(cout, n))
+            ld = torch.full((1,), dl, dtype=torch.int32)
+            xt = torch.from_numpy(x).to(dev)[None].contiguous()
+            wt = torch.from_numpy(w).to(dev)
+            got = torch.from_numpy(go).to(dev)[None].contiguous()
+            out = C.conv333_forward(APRPtrVector([apr]), xt, wt, ld)
+            gi, gw = C.conv333_backward(APRPtrVector([apr]), xt, wt, got, ld)
+            want = o.conv333_forward(x.astype(np.float64), w.astype(np.float64), dl)
+            gi_ref, gw_ref = o.conv333_backward(x.astype(np.float64), w.astype(np.float64), go.astype(np.float64), dl)
+            assert H.rel_err(H.t2n(out[0]), want) <= 5e-3, (taps, wps, cin, cout, dl)
+            assert H.rel_err(H.t2n(gi[0]), gi_ref) <= 5e-3, (taps, wps, cin, cout, dl)
+            assert H.rel_err(H.t2n(gw), gw_ref) <= 5e-3, (taps, wps, cin, cout, dl)
     finally:
-        C.tc_set_option("tma_gather", 0)
+        C.tc_set_option("taps", 0); C.tc_set_option("wps", 0)
