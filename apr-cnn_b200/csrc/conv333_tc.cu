@@ -27,6 +27,8 @@
 #include <algorithm>
 #include <cstring>
 
+extern int g_dw_waves_override;     // defined with the weight-gradient kernel
+
 namespace {
 
 using namespace tcptx;
@@ -276,10 +278,13 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
                 for (int t = 0; t < TAPS; ++t) {
                     if (t0 + t < 27) {
                         const int32_t* idx_t = idx + (t0 + t) * TILE_M;
+                        int32_t src_row[NI];          // read together first: the copy instructions order memory accesses, a read between two of them would wait
+#pragma unroll
+                        for (int i = 0; i < NI; ++i) src_row[i] = idx_t[i * RW];
 #pragma unroll
                         for (int i = 0; i < NI; ++i) {
                             const int row = r0 + i * RW;
-                            cp_async16(smem_u32(a_s + t * A_TAP + row * ROW_BYTES + (swizzled_chunk<KS>(row, j) << 4)), src0 + (ll) idx_t[i * RW] * P.kpad);
+                            cp_async16(smem_u32(a_s + t * A_TAP + row * ROW_BYTES + (swizzled_chunk<KS>(row, j) << 4)), src0 + (ll) src_row[i] * P.kpad);
                         }
                     }
                 }
@@ -650,6 +655,7 @@ extern "C" int aprnet_tc_set_option(const char* name, int value) {
     APRNET_ARG_CHECK(name, "null option name");
     if (!strcmp(name, "taps")) { g_taps_override = value; return APRNET_OK; }
     if (!strcmp(name, "wps")) { g_wps_override = value; return APRNET_OK; }
+    if (!strcmp(name, "dw_waves")) { g_dw_waves_override = value; return APRNET_OK; }
     if (!strcmp(name, "ks")) {
         APRNET_ARG_CHECK(value == 0 || value == 16 || value == 32 || value == 64, "channels per stage must be 0 (automatic), 16, 32 or 64");
         g_ks_override = value;

@@ -21,6 +21,8 @@
 #include <cuda_bf16.h>
 #include <algorithm>
 
+extern int g_dw_waves_override;
+
 namespace {
 
 using namespace tcptx;
@@ -32,12 +34,14 @@ constexpr int A_STAGE = 2 * PT * 128;         // 128 accumulator rows = two 64-e
 
 constexpr int DW_MAX_SEGS = APRNET_MAX_LEVELS;
 struct DwParams {
-    // the levels of the level delta, each split into ranges of range_len locations; range r belongs to the
-    // level i with range_first[i] <= r < range_first[i + 1]
+    // the levels of the level delta, each cut into chunks of PT locations that its blocks take in turn: block r
+    // with range_first[i] <= r < range_first[i + 1] belongs to level i and takes that level's chunks
+    // r - range_first[i], + cnt, + 2 cnt, ... (cnt = blocks of the level).  Blocks that run at the same time
+    // thus walk through the level side by side, and the rows one of them gathers for the neighbouring z planes
+    // are still in L2 when the others (and the blocks of the other tap groups) ask for them.
     int n_segs;
     ll seg_begin[DW_MAX_SEGS], seg_end[DW_MAX_SEGS];
     int range_first[DW_MAX_SEGS + 1];
-    ll range_len;
     const int32_t* nbr; ll N;
     const __nv_bfloat16* xrows; int xpad;  // packed inputs [N + T + 1][xpad]; tree rows start at tree_base, zeros at zero_row
     ll tree_base, zero_row;
@@ -76,9 +80,11 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
     const int MT = (ntaps + TPT - 1) / TPT;             // accumulator tiles of this block
     int seg = 0;
     while (seg + 1 < P.n_segs && (int) blockIdx.x >= P.range_first[seg + 1]) ++seg;
-    const ll pb = P.seg_begin[seg] + (ll) ((int) blockIdx.x - P.range_first[seg]) * P.range_len;
-    const ll pe = min(P.seg_end[seg], pb + P.range_len);
-    const int nchunks = pe > pb ? (int) ((pe - pb + PT - 1) / PT) : 0;
+    const int rl = (int) blockIdx.x - P.range_first[seg], cnt = P.range_first[seg + 1] - P.range_first[seg];
+    const ll pb = P.seg_begin[seg] + (ll) rl * PT, pe = P.seg_end[seg];
+    const ll pstride = (ll) cnt * PT;                   // between two chunks of this block
+    const ll seg_chunks = (pe - P.seg_begin[seg] + PT - 1) / PT;
+    const int nchunks = rl < seg_chunks ? (int) ((seg_chunks - rl + cnt - 1) / cnt) : 0;
     const int total_stages = nchunks * MT;
     const int gpiece = min(256, P.gpad - cob * 256);    // dO channels of this block
 
@@ -109,7 +115,7 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
         // stage is issued, so that the load latency overlaps the copies of the stage in between
         auto request_rows = [&](int s, int32_t (&raw)[TPT]) {
             const int chunk = s / MT, mt = s - chunk * MT;
-            const ll p = pb + (ll) chunk * PT + wq * 32 + lane;
+            const ll p = pb + (ll) chunk * pstride + wq * 32 + lane;
 #pragma unroll
             for (int tl = 0; tl < TPT; ++tl) {
                 const int t = mt * TPT + tl;
@@ -139,7 +145,7 @@ __global__ void __launch_bounds__(DW_THREADS, 1) conv333_tc_dw_kernel(const DwPa
                 const int gc = gpiece / 8;
                 for (int e = lane; e < 32 * gc; e += 32) {
                     const int pl = e / gc, cc = e - pl * gc, k = wq * 32 + pl;
-                    const ll p = pb + (ll) chunk * PT + k;
+                    const ll p = pb + (ll) chunk * pstride + k;
                     cp_async16(smem_u32(g_s + (cc >> 3) * ATOM_STRIDE + k * 128 + (((cc & 7) ^ (k & 7)) << 4)),
                                P.grows + (p < pe ? p : P.g_zero_row) * P.gpad + cob * 256 + cc * 8);
                 }
@@ -266,6 +272,8 @@ int launch_dw(const DwParams& P, int nranges, int blocks_y, cudaStream_t st, con
 
 } // namespace
 
+int g_dw_waves_override = 0;     // aprnet_tc_set_option("dw_waves", n): waves of blocks of the weight gradient, measurement switch
+
 extern "C" int64_t aprnet_conv333_tc_dw_partial_elems(int cin, int cout) {
     const ll per = (ll) 27 * cin * cout;
     const ll ranges = std::max<ll>(32, std::min<ll>(1024, (64ll << 20) / per));     // at least one per level plus room for a wave
@@ -300,23 +308,26 @@ extern "C" int aprnet_conv333_backward_weights_tc(aprnet_apr* a, int dl, int cin
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     char pname[64];
     snprintf(pname, sizeof(pname), "conv333_tc_dw:ci%d:co%d:dl%d", cin, cout, dl);
-    // one launch over all levels: ranges of equal length, enough of them for two waves of one block per SM,
-    // each at least 4 chunks long; a level's ranges are summed into the slot of that level afterwards
+    // one launch over all levels, blocks for `waves` waves of one block per SM where the partial buffer and the number
+    // of levels allow it: every level gets blocks in proportion to its chunks (at most `per_block` chunks each, at least 4
+    // where the level has that many); a level's partial sums are added into the slot of that level afterwards
     const std::vector<Segment> segs = aprnet_segments(a, dl, slots, false);
-    ll total_len = 0;
-    for (const Segment& sg : segs) total_len += sg.end - sg.begin;
-    if (total_len == 0) return APRNET_OK;
-    const int waves = 2;
-    ll want = std::max<ll>(1, ((ll) waves * sms + blocks_y - 1) / blocks_y);
-    want = std::min<ll>(want, (total_len + 4 * PT - 1) / (4 * PT));
-    want = std::max<ll>(1, std::min<ll>(max_ranges - (ll) segs.size(), want));
+    ll total_chunks = 0;
+    for (const Segment& sg : segs) total_chunks += (sg.end - sg.begin + PT - 1) / PT;
+    if (total_chunks == 0) return APRNET_OK;
+    // two waves: a short level then costs a short block rather than an idle SM (1 to 4 waves measured within 5 % of each other)
+    const int waves = g_dw_waves_override > 0 ? g_dw_waves_override : 2;
+    ll budget = std::max<ll>((ll) segs.size(), ((ll) waves * sms + blocks_y - 1) / blocks_y);
+    budget = std::max<ll>(1, std::min<ll>(budget, max_ranges));
+    auto blocks_for = [&](ll per_block) { ll b = 0; for (const Segment& sg : segs) b += ((sg.end - sg.begin + PT - 1) / PT + per_block - 1) / per_block; return b; };
+    ll per_block = std::max<ll>(4, (total_chunks + budget - 1) / budget);
+    while (blocks_for(per_block) > budget) ++per_block;
     DwParams P;
-    P.range_len = ((total_len + want - 1) / want + PT - 1) / PT * PT;
     P.n_segs = (int) segs.size();
     P.range_first[0] = 0;
     for (int i = 0; i < P.n_segs; ++i) {
         P.seg_begin[i] = segs[i].begin; P.seg_end[i] = segs[i].end;
-        P.range_first[i + 1] = P.range_first[i] + (int) ((segs[i].end - segs[i].begin + P.range_len - 1) / P.range_len);
+        P.range_first[i + 1] = P.range_first[i] + (int) (((segs[i].end - segs[i].begin + PT - 1) / PT + per_block - 1) / per_block);
     }
     const int nranges = P.range_first[P.n_segs];
     if (nranges > max_ranges) { aprnet_set_error("conv333 tensor-core weight gradient: %d ranges exceed the partial buffer", nranges); return APRNET_ERR_ARG; }
