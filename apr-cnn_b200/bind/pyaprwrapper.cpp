@@ -507,7 +507,8 @@ void fill_tree_mean_backward_inplace(std::vector<APR*>& aprs, torch::Tensor grad
 }
 
 // ---- 1x1x1 convolution ------------------------------------------------------------------------
-torch::Tensor conv111_forward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights, torch::Tensor level_delta) {
+torch::Tensor conv111_forward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights, torch::Tensor level_delta,
+                              const std::string& precision) {
     CHECK_INPUT(input); CHECK_INPUT(weights);
     check_batch(aprs, input);
     TORCH_CHECK(weights.dim() == 6 && weights.size(3) == 1 && weights.size(4) == 1 && weights.size(5) == 1, "weights must be (stencils, Cout, Cin, 1, 1, 1)");
@@ -517,8 +518,17 @@ torch::Tensor conv111_forward(std::vector<APR*>& aprs, torch::Tensor input, torc
     const int64_t cin = input.size(1), cout = weights.size(1), n = input.size(2);
     auto output = torch::empty({input.size(0), cout, n}, input.options());
     const int dt = dtype_id(input);
+    const bool tc = resolve_mode(precision) == 1 && dt == APRNET_F32;
     for (int64_t b = 0; b < input.size(0); ++b) {
         check_level_delta(*aprs[b], dl[b]);
+        // tensor cores where the layer asks for bf16 arithmetic and the weights fit shared memory; CUDA cores otherwise
+        int rc = APRNET_ERR_UNSUPPORTED;
+        if (tc) {
+            rc = aprnet_conv111_forward_tc(aprs[b]->handle(input), dl[b], (int) cin, (int) cout, (int) weights.size(0), (const float*) row(input, b), n,
+                                           (const float*) weights.data_ptr(), (float*) row(output, b), n, stream_of(input));
+            if (rc != APRNET_ERR_UNSUPPORTED) check(rc, "conv111_forward (tensor cores)");
+        }
+        if (rc == APRNET_ERR_UNSUPPORTED)
         check(aprnet_conv111_forward(aprs[b]->handle(input), dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(input, b), n,
                                      weights.data_ptr(), row(output, b), n, stream_of(input)), "conv111_forward");
         zero_padding(output, b, aprs[b]->number_parts(dl[b]));
@@ -527,7 +537,7 @@ torch::Tensor conv111_forward(std::vector<APR*>& aprs, torch::Tensor input, torc
 }
 
 std::vector<torch::Tensor> conv111_backward(std::vector<APR*>& aprs, torch::Tensor input, torch::Tensor weights,
-                                            torch::Tensor grad_output, torch::Tensor level_delta) {
+                                            torch::Tensor grad_output, torch::Tensor level_delta, const std::string& precision) {
     CHECK_INPUT(input); CHECK_INPUT(weights); CHECK_INPUT(grad_output);
     check_batch(aprs, input);
     TORCH_CHECK(grad_output.dim() == 3 && grad_output.size(1) == weights.size(1) && grad_output.size(2) == input.size(2), "grad_output shape does not match");
@@ -538,10 +548,18 @@ std::vector<torch::Tensor> conv111_backward(std::vector<APR*>& aprs, torch::Tens
     auto grad_weights = torch::zeros_like(weights);
     auto partial = torch::empty({aprnet_conv111_partial_elems((int) cin, (int) cout)}, input.options());
     const int dt = dtype_id(input);
+    const bool tc = resolve_mode(precision) == 1 && dt == APRNET_F32;
     void* st = stream_of(input);
     for (int64_t b = 0; b < input.size(0); ++b) {
         check_level_delta(*aprs[b], dl[b]);
         aprnet_apr* h = aprs[b]->handle(input);
+        int rc = APRNET_ERR_UNSUPPORTED;
+        if (tc) {
+            rc = aprnet_conv111_backward_input_tc(h, dl[b], (int) cin, (int) cout, (int) weights.size(0), (const float*) row(grad_output, b), n,
+                                                  (const float*) weights.data_ptr(), (float*) row(grad_input, b), n, st);
+            if (rc != APRNET_ERR_UNSUPPORTED) check(rc, "conv111_backward_input (tensor cores)");
+        }
+        if (rc == APRNET_ERR_UNSUPPORTED)
         check(aprnet_conv111_backward_input(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(grad_output, b), n,
                                             weights.data_ptr(), row(grad_input, b), n, st), "conv111_backward_input");
         zero_padding(grad_input, b, aprs[b]->number_parts(dl[b]));
@@ -937,8 +955,8 @@ PYBIND11_MODULE(_pyaprwrapper, m) {
     py::module cuda = aprnet.def_submodule("cuda");
     cuda.def("maxpool_forward_cuda", &maxpool_forward_cuda, "aprs"_a, "input"_a, "level_delta"_a);
     cuda.def("maxpool_backward_cuda", &maxpool_backward_cuda, "aprs"_a, "grad_output"_a, "max_indices"_a, "level_delta"_a);
-    cuda.def("conv111_forward", &conv111_forward, "aprs"_a, "input"_a, "weights"_a, "level_delta"_a);
-    cuda.def("conv111_backward", &conv111_backward, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a);
+    cuda.def("conv111_forward", &conv111_forward, "aprs"_a, "input"_a, "weights"_a, "level_delta"_a, "precision"_a = "");
+    cuda.def("conv111_backward", &conv111_backward, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a, "precision"_a = "");
     cuda.def("conv333_forward", &conv333_forward, "aprs"_a, "input"_a, "weights"_a, "level_delta"_a);
     cuda.def("conv333_backward", &conv333_backward, "aprs"_a, "input"_a, "weights"_a, "grad_output"_a, "level_delta"_a);
     // extensions: keep the tree means of the forward pass for the backward pass

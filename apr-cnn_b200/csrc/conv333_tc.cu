@@ -24,6 +24,7 @@
 #include "apr_device.cuh"
 #include "tc_ptx.cuh"
 #include <cuda_bf16.h>
+#include <cuda.h>
 #include <algorithm>
 #include <cstring>
 
@@ -182,8 +183,8 @@ __device__ __forceinline__ TileInfo tile_info(const TcParams& P, int work) {
     return t;
 }
 
-template<int NT, int KS, int TAPS, int WPS, int NACC>
-__global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcParams P, const int stages) {
+template<int NT, int KS, int TAPS, int WPS, int TT, int NACC>
+__global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcParams P, const int stages, const __grid_constant__ CUtensorMap row_map) {
     // A operand: K-major with the hardware swizzle whose width equals the row piece of one stage (KS
     // channels = 32, 64 or 128 bytes).  A gathered row piece is then contiguous in shared memory as it is
     // in global memory (its 16-byte chunks permuted inside the piece), so the lanes that copy one piece
@@ -203,6 +204,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
     constexpr int NTG = (27 + TAPS - 1) / TAPS;              // tap groups per tile
     constexpr uint32_t IDESC = make_idesc(NT, false, false);
     static_assert(WS_NPROD % WPS == 0 && NI >= 1 && WROWS % RW == 0, "a producer warp copies whole instructions");
+    static_assert(TT >= 0 && TT < TAPS || (TT == 0), "the last TT taps of a stage come through the TMA unit, the others through cp.async");
     extern __shared__ __align__(128) unsigned char smem_raw[];
     // swizzle atoms (8 rows) must start on a multiple of their size: align the ring to 1024 bytes
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -267,15 +269,28 @@ __global__ void __launch_bounds__(WS_THREADS, 1) conv333_tc_ws_kernel(const TcPa
                 unsigned char* a_s = stage_base + (size_t) slot * STAGE_BYTES;
                 if (sub == 0 && lane == 0) {
                     const int nt = min(TAPS, 27 - t0);
-                    mbar_expect_tx(smem_u32(full + slot), nt * B_TAP);
+                    mbar_expect_tx(smem_u32(full + slot), nt * B_TAP + max(0, nt - (TAPS - TT)) * A_TAP);
                     for (int t = 0; t < nt; ++t)
                         bulk_copy_g2s(smem_u32(a_s + TAPS * A_TAP + t * B_TAP), wsrc + (ll) (t0 + t) * w_tap_stride + (ll) kc * KS * NT * 2,
                                       B_TAP, smem_u32(full + slot));
                     bulk_issued = true;
                 }
+                if (TT > 0 && sub == WPS - 1) {
+                    // the stage's last TT taps: lane l asks the TMA unit for rows 4l..4l+3 of the tap (tile::gather4 writes
+                    // the same swizzled layout); the bytes count against the arrival that the group's first lane
+                    // announces (a copy that completes earlier only drives the byte count negative until then)
+#pragma unroll
+                    for (int t = TAPS - TT; t < TAPS; ++t) {
+                        if (t0 + t < 27) {
+                            const int4 r = *reinterpret_cast<const int4*>(idx - r0 + (t0 + t) * TILE_M + 4 * lane);
+                            tma_gather4(smem_u32(a_s + t * A_TAP + 4 * lane * ROW_BYTES), &row_map, kc * KS, r.x, r.y, r.z, r.w, smem_u32(full + slot));
+                            bulk_issued = true;
+                        }
+                    }
+                }
                 const __nv_bfloat16* src0 = P.rows + kc * KS + j * 8;
 #pragma unroll
-                for (int t = 0; t < TAPS; ++t) {
+                for (int t = 0; t < TAPS - TT; ++t) {
                     if (t0 + t < 27) {
                         const int32_t* idx_t = idx + (t0 + t) * TILE_M;
                         int32_t src_row[NI];          // read together first: the copy instructions order memory accesses, a read between two of them would wait
@@ -457,7 +472,7 @@ TcGeom tc_geometry(ll rows, int k_dim, int n_dim, int slots) {
 // Stage geometry per tile shape: (taps per stage, producer warps per stage).  The ring needs one slot per producer
 // group plus one for the tensor core; stages are as large as that allows, because the MMA thread pays a fixed
 // ~250 cycles (dependent barrier wait + commit) per stage.
-int g_taps_override = 0, g_wps_override = 0;      // aprnet_tc_set_option("taps" / "wps", n): measurement switches
+int g_taps_override = 0, g_wps_override = 0, g_tma_taps_override = 0;      // aprnet_tc_set_option("taps" / "wps" / "tma_taps", n): measurement switches
 
 constexpr size_t WS_FIXED = (size_t) WS_NIDX * 27 * TILE_M * 4 + (2 * WS_MAX_STAGES + 3 * WS_MAX_ACC) * 8 + 16 + 1024;      // + alignment slack
 constexpr size_t WS_SMEM = 227 * 1024 - 1024;
@@ -475,18 +490,31 @@ inline int ws_stages(int nt, int ks, int taps) {
     X(128, 16, 1, 1) X(128, 16, 3, 2) X(128, 32, 1, 1) X(128, 32, 2, 2) X(128, 32, 3, 4) X(128, 64, 1, 1) X(128, 64, 1, 2) X(128, 64, 2, 4) \
     X(256, 16, 1, 1) X(256, 16, 3, 2) X(256, 32, 1, 1) X(256, 32, 2, 2) X(256, 32, 2, 4)
 
-inline bool tc_variant_ok(int nt, int ks, int taps, int wps) {
+// the same with the last TT taps of every stage fetched by the TMA unit
+#define TC_TMA_VARIANTS(X) \
+    X(32, 32, 3, 2, 1) X(64, 64, 2, 2, 1) X(32, 64, 3, 2, 1)
+
+inline bool tc_variant_ok(int nt, int ks, int taps, int wps, int tt = 0) {
     bool compiled = false;
-#define X(NT_, KS_, TAPS_, WPS_) if (nt == NT_ && ks == KS_ && taps == TAPS_ && wps == WPS_) compiled = true;
+#define X(NT_, KS_, TAPS_, WPS_) if (tt == 0 && nt == NT_ && ks == KS_ && taps == TAPS_ && wps == WPS_) compiled = true;
     TC_VARIANTS(X)
+#undef X
+#define X(NT_, KS_, TAPS_, WPS_, TT_) if (tt == TT_ && nt == NT_ && ks == KS_ && taps == TAPS_ && wps == WPS_) compiled = true;
+    TC_TMA_VARIANTS(X)
 #undef X
     return compiled && ws_stages(nt, ks, taps) >= WS_NPROD / wps + 1;
 }
 
 // default choice: the compiled variant with the most taps per stage whose ring holds all producer groups plus one
 // slot; among equals the one with the fewest warps per stage (more stages in issue at once)
-inline void pick_stage_shape(int nt, int ks, int* taps, int* wps) {
-    if (g_taps_override > 0 && g_wps_override > 0 && tc_variant_ok(nt, ks, g_taps_override, g_wps_override)) { *taps = g_taps_override; *wps = g_wps_override; return; }
+inline void pick_stage_shape(int nt, int ks, bool allow_tma, int* taps, int* wps, int* tt) {
+    *tt = 0;
+    const int tt_want = allow_tma ? g_tma_taps_override : 0;
+    if (g_taps_override > 0 && g_wps_override > 0 && tc_variant_ok(nt, ks, g_taps_override, g_wps_override, tt_want)) {
+        *taps = g_taps_override; *wps = g_wps_override; *tt = tt_want; return;
+    }
+    // 32-channel rows into 32-wide tiles: one of three taps through the TMA unit measured 3-6 % faster than all by cp.async
+    if (allow_tma && nt == 32 && ks == 32 && g_taps_override == 0 && tc_variant_ok(nt, ks, 3, 2, 1)) { *taps = 3; *wps = 2; *tt = 1; return; }
     *taps = 1; *wps = 1;
     static const int tcand[4] = {9, 3, 2, 1}, wcand[3] = {1, 2, 4};
     for (int t : tcand)
@@ -494,11 +522,39 @@ inline void pick_stage_shape(int nt, int ks, int* taps, int* wps) {
             if (tc_variant_ok(nt, ks, t, w)) { *taps = t; *wps = w; return; }
 }
 
-template<int NT, int KS, int TAPS, int WPS>
+// Tensor map of the packed rows [n_rows][kpad] (bf16) with a box of one row piece (ks channels) and the
+// swizzle mode whose span equals the piece: tile::gather4 copies four such pieces per instruction.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int make_row_map(CUtensorMap* map, const void* rows, ll n_rows, int kpad, int ks) {
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+            cudaGetLastError();
+            return APRNET_ERR_UNSUPPORTED;
+        }
+        encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    if ((reinterpret_cast<uintptr_t>(rows) & 15) || n_rows <= 0 || n_rows >= (1ll << 31)) return APRNET_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t) kpad, (cuuint64_t) n_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t) kpad * 2};
+    const cuuint32_t box[2] = {(cuuint32_t) ks, 1};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapSwizzle sw = ks == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : (ks == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(rows), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? APRNET_OK : APRNET_ERR_UNSUPPORTED;
+}
+
+template<int NT, int KS, int TAPS, int WPS, int TT>
 int launch_tc_ws(const TcParams& P, int total_tiles, cudaStream_t st, const char* pname) {
     constexpr size_t STAGE = (size_t) TAPS * ((size_t) TILE_M * KS * 2 + (size_t) NT * KS * 2);
     constexpr int NACC = NT <= 128 ? 4 : 2;          // accumulators in flight: the SM's 512 TMEM columns, at most 4
-    auto kern = conv333_tc_ws_kernel<NT, KS, TAPS, WPS, NACC>;
+    auto kern = conv333_tc_ws_kernel<NT, KS, TAPS, WPS, TT, NACC>;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -508,18 +564,30 @@ int launch_tc_ws(const TcParams& P, int total_tiles, cudaStream_t st, const char
     const size_t smem = (size_t) stages * STAGE + WS_FIXED;
     APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     const int grid = std::min(total_tiles, sms);
+    CUtensorMap row_map;
+    memset(&row_map, 0, sizeof(row_map));
+    // the map ends before the zero row: that coordinate is then out of bounds and the TMA unit fills the piece with
+    // zeros without touching memory
+    if (TT > 0 && make_row_map(&row_map, P.rows, P.zero_row, P.kpad, KS) != APRNET_OK) {
+        aprnet_set_error("conv333 tensor-core path: no tensor map for the packed rows");
+        return APRNET_ERR_UNSUPPORTED;
+    }
     { AprnetProfScope _prof(pname, st);
-    kern<<<grid, WS_THREADS, smem, st>>>(P, stages);
+    kern<<<grid, WS_THREADS, smem, st>>>(P, stages, row_map);
     }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
 }
 
 int dispatch_tc(const TcParams& P, const TcGeom& g, int total_tiles, cudaStream_t st, const char* pname) {
-    int taps = 1, wps = 1;
-    pick_stage_shape(g.nt, g.ks, &taps, &wps);
-#define X(NT_, KS_, TAPS_, WPS_) if (g.nt == NT_ && g.ks == KS_ && taps == TAPS_ && wps == WPS_) return launch_tc_ws<NT_, KS_, TAPS_, WPS_>(P, total_tiles, st, pname);
+    int taps = 1, wps = 1, tt = 0;
+    // the rows of the cross-level pass are addressed from a shifted base with the zero row in front: no tensor map for them
+    pick_stage_shape(g.nt, g.ks, P.out_map == nullptr, &taps, &wps, &tt);
+#define X(NT_, KS_, TAPS_, WPS_) if (tt == 0 && g.nt == NT_ && g.ks == KS_ && taps == TAPS_ && wps == WPS_) return launch_tc_ws<NT_, KS_, TAPS_, WPS_, 0>(P, total_tiles, st, pname);
     TC_VARIANTS(X)
+#undef X
+#define X(NT_, KS_, TAPS_, WPS_, TT_) if (tt == TT_ && g.nt == NT_ && g.ks == KS_ && taps == TAPS_ && wps == WPS_) return launch_tc_ws<NT_, KS_, TAPS_, WPS_, TT_>(P, total_tiles, st, pname);
+    TC_TMA_VARIANTS(X)
 #undef X
     aprnet_set_error("conv333 tensor-core path: unsupported tile geometry nt=%d ks=%d taps=%d wps=%d", g.nt, g.ks, taps, wps);
     return APRNET_ERR_UNSUPPORTED;
@@ -655,6 +723,7 @@ extern "C" int aprnet_tc_set_option(const char* name, int value) {
     APRNET_ARG_CHECK(name, "null option name");
     if (!strcmp(name, "taps")) { g_taps_override = value; return APRNET_OK; }
     if (!strcmp(name, "wps")) { g_wps_override = value; return APRNET_OK; }
+    if (!strcmp(name, "tma_taps")) { g_tma_taps_override = value; return APRNET_OK; }
     if (!strcmp(name, "dw_waves")) { g_dw_waves_override = value; return APRNET_OK; }
     if (!strcmp(name, "ks")) {
         APRNET_ARG_CHECK(value == 0 || value == 16 || value == 32 || value == 64, "channels per stage must be 0 (automatic), 16, 32 or 64");

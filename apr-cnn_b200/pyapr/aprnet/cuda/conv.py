@@ -66,10 +66,11 @@ class Conv111Function(Function):
     """1x1x1 stencil: a per-level channel mix, no neighbour access and no stencil expansion."""
 
     @staticmethod
-    def forward(ctx, inputs, weights, bias, aprs, level_deltas):
+    def forward(ctx, inputs, weights, bias, aprs, level_deltas, precision=None):
         ctx.aprs = aprs
+        ctx.precision = precision or ""
         ctx.save_for_backward(inputs, weights, bias, level_deltas.clone())
-        out = conv111_forward(APRPtrVector(aprs), inputs, weights, level_deltas)
+        out = conv111_forward(APRPtrVector(aprs), inputs, weights, level_deltas, ctx.precision)
         if bias is not None:
             out = out + bias.view(1, -1, 1)
         return out
@@ -78,16 +79,16 @@ class Conv111Function(Function):
     def backward(ctx, grad_output):
         inputs, weights, bias, level_deltas = ctx.saved_tensors
         grad_output = grad_output.contiguous()
-        grad_input, grad_weights = conv111_backward(APRPtrVector(ctx.aprs), inputs, weights, grad_output, level_deltas)
+        grad_input, grad_weights = conv111_backward(APRPtrVector(ctx.aprs), inputs, weights, grad_output, level_deltas, ctx.precision)
         grad_bias = grad_output.sum(dim=(0, 2)) if bias is not None else None
-        return grad_input, grad_weights, grad_bias, None, None
+        return grad_input, grad_weights, grad_bias, None, None, None
 
 
 _FUNCTIONS = {(1, 1, 1): Conv111Function, (3, 3, 3): Conv333Function}
 
 
 class APRConv(nn.Module):
-    """`precision` (not in the reference): arithmetic of a 3x3x3 layer on float32 tensors, "fp32" (CUDA-core kernels,
+    """`precision` (not in the reference): arithmetic of the layer on float32 tensors, "fp32" (CUDA-core kernels,
     exact) or "bf16" (tensor cores, bf16 operands with fp32 accumulation); None follows the process-wide setting
     (`set_conv_precision`)."""
 
@@ -119,6 +120,4 @@ class APRConv(nn.Module):
             init.uniform_(self.bias, -bound, bound)
 
     def forward(self, input_features, aprs, level_deltas):
-        if self.kernel_size == (3, 3, 3):
-            return self._function.apply(input_features, self.weight, self.bias, aprs, level_deltas, self.precision)
-        return self._function.apply(input_features, self.weight, self.bias, aprs, level_deltas)
+        return self._function.apply(input_features, self.weight, self.bias, aprs, level_deltas, self.precision)

@@ -216,7 +216,9 @@ void aprnet_tc_error_reset(void);
 int aprnet_tc_selftest_wait_timeout(int max_polls, void* stream);
 /* Measurement switches of the tensor-core gather kernel (0 = automatic): "taps" = taps of the 27 per shared-memory
  * stage, "wps" = producer warps that fill one stage together (both must be set, and the pair must be a compiled
- * shape whose ring fits shared memory, else the automatic choice stays), "ks" = channels per stage (16, 32, 64). */
+ * shape whose ring fits shared memory, else the automatic choice stays), "tma_taps" = how many of a stage's taps the TMA
+ * unit fetches (tile::gather4) instead of cp.async (with "taps" and "wps"), "ks" = channels per stage (16, 32, 64),
+ * "dw_waves" = waves of blocks of the weight-gradient kernel. */
 int aprnet_tc_set_option(const char* name, int value);
 
 /* ---- 1x1x1 convolution -----------------------------------------------------------------------
@@ -228,6 +230,15 @@ int aprnet_conv111_forward(const aprnet_apr* apr, int level_delta, int dtype, in
 int aprnet_conv111_backward_input(const aprnet_apr* apr, int level_delta, int dtype, int cin, int cout,
                                   int num_stencils, const void* grad_output, int64_t ld_out, const void* weights,
                                   void* grad_input, int64_t ld_in, void* stream);
+/* The same two products with bf16 operands and fp32 accumulation on the tensor cores (float32 tensors, the layer's
+ * precision "bf16"): replaces the same launchers, conv111_gpu.cu:175-232.  APRNET_ERR_UNSUPPORTED when a channel count
+ * exceeds 256 or is below 8, or the level's weights plus two operand stages do not fit shared memory: call the entry
+ * above then. */
+int aprnet_conv111_forward_tc(const aprnet_apr* apr, int level_delta, int cin, int cout, int num_stencils,
+                              const float* input, int64_t ld_in, const float* weights, float* output, int64_t ld_out, void* stream);
+int aprnet_conv111_backward_input_tc(const aprnet_apr* apr, int level_delta, int cin, int cout, int num_stencils,
+                                     const float* grad_output, int64_t ld_out, const float* weights, float* grad_input, int64_t ld_in,
+                                     void* stream);
 int64_t aprnet_conv111_partial_elems(int cin, int cout);
 int aprnet_conv111_backward_weights(const aprnet_apr* apr, int level_delta, int dtype, int cin, int cout,
                                     int num_stencils, const void* input, int64_t ld_in, const void* grad_output,

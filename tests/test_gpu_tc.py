@@ -67,10 +67,10 @@ def test_conv333_tensor_core_path(name, cin, cout, nst, oracle, bf16_mode):
             assert H.rel_err(H.t2n(gw), gw_ref) <= tol_out, (name, dl, exact_inputs)
 
 
-@pytest.mark.parametrize("taps,wps", [(1, 1), (3, 1), (3, 2), (3, 4), (2, 4), (9, 4)])
-def test_conv333_stage_shape_variants(taps, wps, oracle, bf16_mode):
-    """Every compiled stage shape of the gather kernel (taps per stage, producer warps per stage) gives the same
-    parity; shapes that do not exist for a tile geometry fall back to the automatic choice."""
+@pytest.mark.parametrize("taps,wps,tma_taps", [(1, 1, 0), (3, 1, 0), (3, 2, 0), (3, 4, 0), (2, 4, 0), (9, 4, 0), (3, 2, 1), (2, 2, 1)])
+def test_conv333_stage_shape_variants(taps, wps, tma_taps, oracle, bf16_mode):
+    """Every compiled stage shape of the gather kernel (taps per stage, producer warps per stage, taps fetched by the TMA
+    unit) gives the same parity; shapes that do not exist for a tile geometry fall back to the automatic choice."""
     import pyapr
     from _pyaprwrapper.data_containers import APRPtrVector
     C = bf16_mode
@@ -81,7 +81,7 @@ def test_conv333_stage_shape_variants(taps, wps, oracle, bf16_mode):
     o = oracle.OracleAPR(a)
     L = a.level_max - a.level_min + 1
     rng = np.random.RandomState(5)
-    C.tc_set_option("taps", taps); C.tc_set_option("wps", wps)
+    C.tc_set_option("taps", taps); C.tc_set_option("wps", wps); C.tc_set_option("tma_taps", tma_taps)
     try:
         for cin, cout, dl in [(32, 32, 0), (64, 64, 0), (64, 32, 1), (16, 48, 0), (128, 130, 1)]:
             n = o.number_parts(dl)
@@ -98,4 +98,49 @@ def test_conv333_stage_shape_variants(taps, wps, oracle, bf16_mode):
             assert H.rel_err(H.t2n(gi[0]), gi_ref) <= 5e-3, (taps, wps, cin, cout, dl)
             assert H.rel_err(H.t2n(gw), gw_ref) <= 5e-3, (taps, wps, cin, cout, dl)
     finally:
-        C.tc_set_option("taps", 0); C.tc_set_option("wps", 0)
+        C.tc_set_option("taps", 0); C.tc_set_option("wps", 0); C.tc_set_option("tma_taps", 0)
+
+
+@pytest.mark.parametrize("cin,cout,nst", [(64, 32, 2), (32, 2, 2), (2, 32, 1), (40, 19, 6), (256, 128, 2), (128, 256, 1), (72, 130, 3), (1, 1, 1)])
+@pytest.mark.parametrize("name", ["blob", "odd", "multi_tile"])
+def test_conv111_tensor_core_path(name, cin, cout, nst, oracle, bf16_mode):
+    """1x1x1 convolution on the tensor cores (forward and input gradient; the weight gradient stays on the CUDA cores)
+    against the float64 oracle: bf16-exact operands leave only the fp32 accumulation order."""
+    import pyapr
+    from _pyaprwrapper.data_containers import APRPtrVector
+    C = bf16_mode
+    dev = torch.device("cuda:0")
+    a = H.blob_arrays((64, 128, 128), 40, 11) if name == "multi_tile" else (H.arrays(name) if name in H.APR_CASES else H.blob_arrays())
+    apr = pyapr.apr_from_arrays(a, name)
+    apr.init_cuda()
+    o = oracle.OracleAPR(a)
+    rng = np.random.RandomState(17)
+    for dl in range(0, min(H.max_dl(a), 2) + 1):
+        n = o.number_parts(dl)
+        ld = torch.full((1,), dl, dtype=torch.int32)
+        for exact_inputs in (True, False):
+            x = rng.rand(cin, n).astype(np.float32)
+            w = (rng.randn(nst, cout, cin, 1, 1, 1) / np.sqrt(cin)).astype(np.float32)
+            go = rng.randn(cout, n).astype(np.float32)
+            if exact_inputs:
+                x, w, go = bf16_round(x), bf16_round(w), bf16_round(go)
+            xt = torch.from_numpy(x).to(dev)[None].contiguous()
+            wt = torch.from_numpy(w).to(dev)
+            got = torch.from_numpy(go).to(dev)[None].contiguous()
+            C.profile_read(); C.profile_enable(True)
+            out = C.conv111_forward(APRPtrVector([apr]), xt, wt, ld)
+            gi, gw = C.conv111_backward(APRPtrVector([apr]), xt, wt, got, ld)
+            torch.cuda.synchronize()
+            C.profile_enable(False)
+            names = set(k.split(":")[0] for k in C.profile_read())
+            # the tensor-core kernel ran unless the layer is narrower than 8 channels on either side (those stay on the CUDA cores)
+            assert ("conv111_tc" in names) == (min(cin, cout) >= 8), names
+            want = o.conv111_forward(x.astype(np.float64), w.astype(np.float64), dl)
+            gi_ref, gw_ref = o.conv111_backward(x.astype(np.float64), w.astype(np.float64), go.astype(np.float64), dl)
+            tol = 2e-5 if (exact_inputs or min(cin, cout) < 8) else 2e-2
+            assert H.rel_err(H.t2n(out[0]), want) <= tol, (name, dl, exact_inputs)
+            assert H.rel_err(H.t2n(gi[0]), gi_ref) <= tol, (name, dl, exact_inputs)
+            assert H.rel_err(H.t2n(gw), gw_ref) <= 1e-5, (name, dl, exact_inputs)
+            # an explicit per-call precision overrides the process-wide setting
+            out32 = C.conv111_forward(APRPtrVector([apr]), xt, wt, ld, "fp32")
+            assert H.rel_err(H.t2n(out32[0]), want) <= 1e-5
