@@ -125,35 +125,52 @@ __global__ void lower_bound_kernel(const int32_t* __restrict__ sorted, ll n, con
     out[k] = lo;
 }
 
-// pass 1: thread = (virtual row, 8-channel chunk); sums the dO rows of the row's locations in ascending
-// order (fp32) and writes the bf16 row 1 + v - v0 of the workspace (row 0 is the zero row)
-__global__ void vrow_reduce_kernel(const int32_t* __restrict__ vstart, const int32_t* __restrict__ vsrc, ll v0, ll v1,
-                                   const __nv_bfloat16* __restrict__ grows, int gpad, __nv_bfloat16* __restrict__ out) {
+// pass 1: thread = (VPT consecutive virtual rows, 8-channel chunk); sums the dO rows of each row's locations in
+// ascending order (fp32) and writes the bf16 row 1 + v - v0 of the workspace (row 0 is the zero row).  The three
+// dependent accesses (row starts -> source locations -> dO rows) are each requested for all VPT rows and up to four
+// locations per row before any is used (runs are 1-4 locations long; longer ones continue in a loop).
+constexpr int VROW_VPT = 2;          // measured: 2 rows per thread 20 % faster than 1, 4 slower (registers)
+
+template<int VPT>
+__global__ void __launch_bounds__(256) vrow_reduce_kernel(const int32_t* __restrict__ vstart, const int32_t* __restrict__ vsrc, ll v0, ll v1,
+                                                          const __nv_bfloat16* __restrict__ grows, int gpad, __nv_bfloat16* __restrict__ out) {
     const int nch = gpad >> 3;
     const ll e = (ll) blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= (v1 - v0) * nch) return;
-    const ll v = v0 + e / nch;
+    const ll vb = v0 + (e / nch) * VPT;
+    if (vb >= v1) return;
     const int c = (int) (e % nch);
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    const int e1 = vstart[v + 1];
-    for (int i = vstart[v]; i < e1; i += 4) {          // four rows requested before any is added (runs are 1-4 rows long)
-        int32_t src[4];
-        uint4 q[4];
+    int s[VPT + 1];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) src[u] = i + u < e1 ? __ldg(vsrc + i + u) : -1;
+    for (int u = 0; u <= VPT; ++u) s[u] = __ldg(vstart + min(vb + u, v1));
+    int32_t src[VPT][4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) q[u] = src[u] >= 0 ? __ldg(reinterpret_cast<const uint4*>(grows + (ll) src[u] * gpad + c * 8)) : make_uint4(0, 0, 0, 0);
+    for (int u = 0; u < VPT; ++u)
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {                   // ascending location order
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q[u]);
+        for (int k = 0; k < 4; ++k) src[u][k] = s[u] + k < s[u + 1] ? __ldg(vsrc + s[u] + k) : -1;
+    uint4 q[VPT][4];
+#pragma unroll
+    for (int u = 0; u < VPT; ++u)
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            q[u][k] = src[u][k] >= 0 ? __ldg(reinterpret_cast<const uint4*>(grows + (ll) src[u][k] * gpad + c * 8)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+        if (vb + u >= v1) break;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        auto add = [&](const uint4& r) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
 #pragma unroll
             for (int k = 0; k < 4; ++k) { const float2 f = __bfloat1622float2(h[k]); acc[2 * k] += f.x; acc[2 * k + 1] += f.y; }
-        }
-    }
-    __nv_bfloat162 o[4];
+        };
 #pragma unroll
-    for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
-    *reinterpret_cast<uint4*>(out + (1 + v - v0) * gpad + c * 8) = *reinterpret_cast<const uint4*>(o);
+        for (int k = 0; k < 4; ++k) add(q[u][k]);              // ascending location order (absent entries add zeros)
+        for (int i = s[u] + 4; i < s[u + 1]; ++i)
+            add(__ldg(reinterpret_cast<const uint4*>(grows + (ll) __ldg(vsrc + i) * gpad + c * 8)));
+        __nv_bfloat162 o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+        *reinterpret_cast<uint4*>(out + (1 + vb + u - v0) * gpad + c * 8) = *reinterpret_cast<const uint4*>(o);
+    }
 }
 
 constexpr ll VROW_GRANULE = 4ll << 20;      // virtual rows per entry of the chunk map
@@ -350,8 +367,8 @@ int aprnet_cross_level_tc(aprnet_apr* a, int dl, int cin, int cout, int slots, c
             if (v1 - v0 > cap_rows) { aprnet_set_error("edge workspace too small for %lld virtual rows", v1 - v0); return APRNET_ERR_ARG; }
             if (v1 > v0) {
                 { AprnetProfScope _prof("edge_reduce", st);
-                vrow_reduce_kernel<<<aprnet_ceil_div((v1 - v0) * (gpad / 8), 256), 256, 0, st>>>(ep->vstart, ep->vsrc, v0, v1,
-                                                                                            (const __nv_bfloat16*) grows, gpad, vrows);
+                vrow_reduce_kernel<VROW_VPT><<<aprnet_ceil_div(aprnet_ceil_div(v1 - v0, VROW_VPT) * (gpad / 8), 256), 256, 0, st>>>(
+                    ep->vstart, ep->vsrc, v0, v1, (const __nv_bfloat16*) grows, gpad, vrows);
                 }
                 APRNET_LAUNCH_CHECK();
                 // row index r of the gather = virtual row id; the zero row is addressed as v0 - 1
