@@ -161,9 +161,9 @@ def unet_conv_layers(base, depth):
 
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture per kernel family on the 64->64
-# layer at level_delta 1 of a 256x512x512 volume, 1.77 M locations) divided by the algorithmic bytes of the
+# layer at level_delta 1 of a 256x512x512 volume, 1.86 M locations) divided by the algorithmic bytes of the
 # same operator call.  Every operand of these kernels is streamed, so traffic scales with the locations.
-NCU_TRAFFIC_RATIO = {"conv333_tc_dw": 2.72, "conv333_tc_fwd": 1.36, "conv333_tc_bwd_gather": 1.29}
+NCU_TRAFFIC_RATIO = {"conv333_tc_dw": 2.11, "conv333_tc_fwd": 1.36, "conv333_tc_bwd_gather": 1.29}
 
 
 GN_BYTES = {"groupnorm_stats": 4.0, "groupnorm_relu_apply": 8.0, "groupnorm_bwd_reduce": 8.0, "groupnorm_bwd_apply": 12.0}
@@ -272,7 +272,7 @@ def roofline_from_profile(prof, steps, nparts, ntree, peaks, layers, bf16):
               hbm_gbs_at_algorithmic_bytes=byts / sec / 1e9, peak_source=peaks["source"],
               traffic=(byts / max(1, launches)) * NCU_TRAFFIC_RATIO[fam] if fam in NCU_TRAFFIC_RATIO else None,
               traffic_source="algorithmic bytes x the dram__bytes ratio of an ncu capture of this kernel on the 64->64 layer at level_delta 1 of a "
-                             "256x512x512 volume (1.77 M locations), scaled by locations" if fam in NCU_TRAFFIC_RATIO else None)
+                             "256x512x512 volume (1.86 M locations), scaled by locations" if fam in NCU_TRAFFIC_RATIO else None)
     return rf
 
 
