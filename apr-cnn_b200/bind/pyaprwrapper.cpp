@@ -563,6 +563,14 @@ std::vector<torch::Tensor> conv111_backward(std::vector<APR*>& aprs, torch::Tens
         check(aprnet_conv111_backward_input(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(grad_output, b), n,
                                             weights.data_ptr(), row(grad_input, b), n, st), "conv111_backward_input");
         zero_padding(grad_input, b, aprs[b]->number_parts(dl[b]));
+        rc = APRNET_ERR_UNSUPPORTED;
+        if (tc) {
+            rc = aprnet_conv111_backward_weights_tc(h, dl[b], (int) cin, (int) cout, (int) weights.size(0), (const float*) row(input, b), n,
+                                                    (const float*) row(grad_output, b), n, (float*) grad_weights.data_ptr(),
+                                                    (float*) partial.data_ptr(), partial.numel(), st);
+            if (rc != APRNET_ERR_UNSUPPORTED) check(rc, "conv111_backward_weights (tensor cores)");
+        }
+        if (rc == APRNET_ERR_UNSUPPORTED)
         check(aprnet_conv111_backward_weights(h, dl[b], dt, (int) cin, (int) cout, (int) weights.size(0), row(input, b), n,
                                               row(grad_output, b), n, grad_weights.data_ptr(), partial.data_ptr(), st),
               "conv111_backward_weights");

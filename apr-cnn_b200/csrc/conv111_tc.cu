@@ -32,6 +32,7 @@ using namespace tcptx;
 typedef long long ll;
 constexpr int TILE_M = 128;
 constexpr int C1_THREADS = 17 * 32;
+constexpr int C1_THREADS_DW = 13 * 32;
 constexpr int C1_MAX_STAGES = 8;
 constexpr int C1_MAX_ACC = 4;
 constexpr int C1_MAX_SEGS = APRNET_MAX_LEVELS;
@@ -266,6 +267,175 @@ int run_conv111_tc(const aprnet_apr* a, int dl, int n_in, int n_out, int slots, 
     return APRNET_ERR_UNSUPPORTED;
 }
 
+
+// ---- weight gradient -----------------------------------------------------------------------------------
+// gw[slot][o][i] += sum over the locations p of the slot's levels of gout[o][p] * in[i][p]: M = output channels (padded
+// to 128 per accumulator), N = input channels, K = locations.  Both tensors are channel-major, i.e. K-major operands
+// as they lie in memory; they only have to be rounded to bf16.  One persistent block per SM walks its share of the
+// 128-location tiles of ONE level range and keeps the accumulators in TMEM until the end:
+//   warps 0-7   producers: a warp takes channel rows of both tensors in turn, 32 consecutive locations per load
+//               instruction (coalesced), and writes each value as a 2-byte piece of the swizzled K-major operand row
+//               (conflict-free: the 32 lanes fill 64 bytes of one 128-byte row); locations past the end are zeros;
+//   warp 8      one thread issues 8 tcgen05.mma per accumulator and stage;
+//   warps 9-12  after the last tile: TMEM -> partial sums of this block; a second kernel adds the blocks in fixed order.
+struct C1DwParams {
+    ll seg_begin, seg_end;
+    const float* in; ll ld_in; int cin;
+    const float* gout; ll ld_out; int cout;
+    float* partial;                         // [block][cout][cin]
+    int* error_flag;
+};
+
+template<int NT>
+__global__ void __launch_bounds__(C1_THREADS_DW, 1) conv111_tc_dw_kernel(const C1DwParams P, const int stages, const int mtiles) {
+    constexpr int SUB = 64;                                  // locations per swizzle atom row (128 bytes)
+    constexpr uint32_t IDESC = make_idesc(NT, false, false);
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const int a_rows = mtiles * 128;
+    const int stage_bytes = (a_rows + NT) * 256;             // two 64-location halves of 128 bytes per channel row
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t) stages * stage_bytes);
+    uint64_t* full = bars;                                   // [stages] operands written (256 producer threads)
+    uint64_t* empty = bars + C1_MAX_STAGES;                  // [stages] MMAs that read the stage completed
+    uint64_t* done = empty + C1_MAX_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t tmem_cols = mtiles * NT <= 32 ? 32u : (mtiles * NT <= 64 ? 64u : (mtiles * NT <= 128 ? 128u : (mtiles * NT <= 256 ? 256u : 512u)));
+    if (tid == 0) {
+        for (int i = 0; i < stages; ++i) { mbar_init(smem_u32(full + i), 256); mbar_init(smem_u32(empty + i), 1); }
+        mbar_init(smem_u32(done), 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 8) { tmem_alloc(smem_u32(tmem_slot), tmem_cols); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_d = *tmem_slot;
+    bool failed = false;
+    const ll sb = P.seg_begin, se = P.seg_end;
+    const int seg_tiles = (int) ((se - sb + TILE_M - 1) / TILE_M);
+    const int mine = (int) blockIdx.x < seg_tiles ? (seg_tiles - (int) blockIdx.x + (int) gridDim.x - 1) / (int) gridDim.x : 0;
+
+    if (warp < 8) {
+        // ---------------- producers ----------------
+        const int nrows = P.cout + P.cin;                    // channel rows of a stage: gout rows, then in rows
+        for (int it = 0; it < mine && !failed; ++it) {
+            const uint32_t slot = (uint32_t) it % (uint32_t) stages, use = (uint32_t) it / (uint32_t) stages;
+            const ll p0 = sb + ((ll) blockIdx.x + (ll) it * gridDim.x) * TILE_M;
+            if (use > 0 && !mbar_wait_warp(smem_u32(empty + slot), (use - 1) & 1, abort_flag)) { failed = true; break; }
+            unsigned char* st = smem + (size_t) slot * stage_bytes;
+            for (int r0 = warp; r0 < nrows; r0 += 8 * 8) {   // 8 rows of this warp x 4 quarters of 32 locations in flight
+                float v[8][4];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int r = r0 + u * 8;
+                    const float* src = r < P.cout ? P.gout + (ll) r * P.ld_out : P.in + (ll) (r - P.cout) * P.ld_in;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const ll p = p0 + q * 32 + lane;
+                        v[u][q] = (r < nrows && p < se) ? src[p] : 0.f;
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int r = r0 + u * 8;
+                    if (r >= nrows) break;
+                    // operand row: gout rows first (accumulator rows), in rows after a_rows
+                    const int orow = r < P.cout ? r : a_rows + (r - P.cout);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int pl = q * 32 + lane;                     // location within the tile
+                        const int half = pl / SUB, k = pl % SUB;
+                        unsigned char* dst = st + (size_t) half * ((size_t) (a_rows + NT) * 128) + (size_t) orow * 128
+                                           + ((((k >> 3) ^ (orow & 7)) << 4) | ((k & 7) << 1));
+                        *reinterpret_cast<__nv_bfloat16*>(dst) = __float2bfloat16(v[u][q]);
+                    }
+                }
+            }
+            mbar_arrive(smem_u32(full + slot));               // the MMA thread fences the generic-proxy writes after its wait
+        }
+    } else if (warp == 8) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            for (int it = 0; it < mine && !failed; ++it) {
+                const uint32_t slot = (uint32_t) it % (uint32_t) stages, use = (uint32_t) it / (uint32_t) stages;
+                if (!mbar_wait(smem_u32(full + slot), use & 1, abort_flag)) { failed = true; break; }
+                fence_proxy_async();
+                tc_fence_after();
+                const uint32_t base = smem_u32(smem + (size_t) slot * stage_bytes);
+                for (int half = 0; half < 2; ++half) {
+                    const uint32_t hb = base + half * ((a_rows + NT) * 128);
+                    const uint64_t db0 = make_desc(hb + a_rows * 128, 16, 1024, 2);
+                    for (int mt = 0; mt < mtiles; ++mt) {
+                        const uint64_t da0 = make_desc(hb + mt * 128 * 128, 16, 1024, 2);
+#pragma unroll
+                        for (int k = 0; k < SUB / 16; ++k)
+                            umma_bf16(tmem_d + mt * NT, da0 + (uint64_t) ((k * 32) >> 4), db0 + (uint64_t) ((k * 32) >> 4), IDESC,
+                                      (it > 0 || half > 0 || k > 0) ? 1u : 0u);
+                    }
+                }
+                umma_commit(smem_u32(empty + slot));
+            }
+            if (!failed) umma_commit(smem_u32(done));
+        }
+    }
+    // ---------------- epilogue: warps 9-12 ----------------
+    float* dst = P.partial + (ll) blockIdx.x * P.cout * P.cin;
+    if (warp >= 9 && mine > 0 && !failed) {
+        if (!mbar_wait_warp(smem_u32(done), 0, abort_flag)) failed = true;
+        if (!failed) {
+            tc_fence_after();
+            const int q = warp & 3, row = q * 32 + lane;
+            for (int mt = 0; mt < mtiles; ++mt) {
+                const int o = mt * 128 + row;
+#pragma unroll
+                for (int c0 = 0; c0 < NT; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_d + ((uint32_t) (q * 32) << 16) + mt * NT + c0, r);
+                    tmem_ld_wait();
+                    if (o < P.cout) {
+#pragma unroll
+                        for (int jj = 0; jj < 32; ++jj)
+                            if (c0 + jj < P.cin) dst[(ll) o * P.cin + c0 + jj] = __uint_as_float(r[jj]);
+                    }
+                }
+            }
+        }
+    } else if (mine == 0) {
+        for (int e = tid; e < P.cout * P.cin; e += C1_THREADS_DW) dst[e] = 0.f;       // this block still owns its slice
+    }
+    if (failed) {
+        *abort_flag = 1;
+        if (P.error_flag) *P.error_flag = 1;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) tmem_dealloc(tmem_d, tmem_cols);
+}
+
+__global__ void c1_reduce_partial_kernel(const float* __restrict__ partial, int nblocks, ll elems, float* __restrict__ dst) {
+    const ll e = (ll) blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= elems) return;
+    float s = 0.f;
+    for (int c = 0; c < nblocks; ++c) s += partial[(ll) c * elems + e];
+    dst[e] += s;
+}
+
+template<int NT>
+int launch_c1_dw(const C1DwParams& P, int grid, int mtiles, cudaStream_t st) {
+    const size_t stage = (size_t) (mtiles * 128 + NT) * 256;
+    const size_t fixed = (2 * C1_MAX_STAGES + 1) * 8 + 16 + 1024;
+    if (fixed + 2 * stage > 227 * 1024 - 1024) return APRNET_ERR_UNSUPPORTED;
+    const int stages = (int) std::min<size_t>(C1_MAX_STAGES, (227 * 1024 - 1024 - fixed) / stage);
+    const size_t smem = (size_t) stages * stage + fixed;
+    auto kern = conv111_tc_dw_kernel<NT>;
+    APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    kern<<<grid, C1_THREADS_DW, smem, st>>>(P, stages, mtiles);
+    return APRNET_OK;
+}
+
 } // namespace
 
 extern "C" int aprnet_conv111_forward_tc(const aprnet_apr* a, int dl, int cin, int cout, int S, const float* in, int64_t ld_in,
@@ -286,4 +456,45 @@ extern "C" int aprnet_conv111_backward_input_tc(const aprnet_apr* a, int dl, int
     char pname[64];
     snprintf(pname, sizeof(pname), "conv111_tc:ci%d:co%d:dl%d", cout, cin, dl);
     return run_conv111_tc(a, dl, cout, cin, S, gout, ld_out, w, (ll) cin * cout, 1, cin, gin, ld_in, (cudaStream_t) stream, pname);
+}
+
+extern "C" int aprnet_conv111_backward_weights_tc(const aprnet_apr* a, int dl, int cin, int cout, int S, const float* in, int64_t ld_in,
+                                                  const float* gout, int64_t ld_out, float* gw, float* partial, int64_t partial_elems,
+                                                  void* stream) {
+    APRNET_ARG_CHECK(a && a->valid_dl(dl) && in && gout && gw && partial && cin > 0 && cout > 0 && S > 0, "bad argument");
+    APRNET_DEVICE_CHECK(a);
+    APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl), "leading dimension too small");
+    if (cin > 256 || cout > 256 || cin < 8 || cout < 8) return APRNET_ERR_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t) stream;
+    const ll elems = (ll) cin * cout;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int max_blocks = (int) std::min<ll>(sms, partial_elems / elems);
+    if (max_blocks < 1) return APRNET_ERR_UNSUPPORTED;
+    const int nt = pick_nt(cin), mtiles = (cout + 127) / 128;
+    if (mtiles * nt > 512) return APRNET_ERR_UNSUPPORTED;
+    for (const Segment& sg : aprnet_segments(a, dl, S, true)) {
+        if (sg.end <= sg.begin) continue;
+        C1DwParams P;
+        P.seg_begin = sg.begin; P.seg_end = sg.end; P.in = in; P.ld_in = ld_in; P.cin = cin; P.gout = gout; P.ld_out = ld_out; P.cout = cout;
+        P.partial = partial; P.error_flag = aprnet_tc_error_flag_device();
+        const int grid = (int) std::min<ll>(max_blocks, (sg.end - sg.begin + TILE_M - 1) / TILE_M);
+        int rc = APRNET_ERR_UNSUPPORTED;
+        { AprnetProfScope _prof("conv111_tc_dw", st);
+        switch (nt) {
+            case 16: rc = launch_c1_dw<16>(P, grid, mtiles, st); break;
+            case 32: rc = launch_c1_dw<32>(P, grid, mtiles, st); break;
+            case 64: rc = launch_c1_dw<64>(P, grid, mtiles, st); break;
+            case 128: rc = launch_c1_dw<128>(P, grid, mtiles, st); break;
+            case 256: rc = launch_c1_dw<256>(P, grid, mtiles, st); break;
+        }
+        }
+        if (rc) return rc;
+        { AprnetProfScope _prof("conv111_dw_reduce", st);
+        c1_reduce_partial_kernel<<<aprnet_ceil_div(elems, 256), 256, 0, st>>>(partial, grid, elems, gw + (ll) sg.slot * elems);
+        }
+    }
+    APRNET_LAUNCH_CHECK();
+    return APRNET_OK;
 }

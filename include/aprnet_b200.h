@@ -239,6 +239,11 @@ int aprnet_conv111_forward_tc(const aprnet_apr* apr, int level_delta, int cin, i
 int aprnet_conv111_backward_input_tc(const aprnet_apr* apr, int level_delta, int cin, int cout, int num_stencils,
                                      const float* grad_output, int64_t ld_out, const float* weights, float* grad_input, int64_t ld_in,
                                      void* stream);
+/* Weight gradient of the 1x1x1 convolution with bf16 operands on the tensor cores (accumulated into grad_weights, float32
+ * (num_stencils, Cout, Cin)); partial: aprnet_conv111_partial_elems() floats, partial_elems its size.  Same fallback rule. */
+int aprnet_conv111_backward_weights_tc(const aprnet_apr* apr, int level_delta, int cin, int cout, int num_stencils,
+                                       const float* input, int64_t ld_in, const float* grad_output, int64_t ld_out,
+                                       float* grad_weights, float* partial, int64_t partial_elems, void* stream);
 int64_t aprnet_conv111_partial_elems(int cin, int cout);
 int aprnet_conv111_backward_weights(const aprnet_apr* apr, int level_delta, int dtype, int cin, int cout,
                                     int num_stencils, const void* input, int64_t ld_in, const void* grad_output,
