@@ -464,7 +464,7 @@ extern "C" int aprnet_conv111_backward_weights_tc(const aprnet_apr* a, int dl, i
     APRNET_ARG_CHECK(a && a->valid_dl(dl) && in && gout && gw && partial && cin > 0 && cout > 0 && S > 0, "bad argument");
     APRNET_DEVICE_CHECK(a);
     APRNET_ARG_CHECK(ld_in >= a->number_parts(dl) && ld_out >= a->number_parts(dl), "leading dimension too small");
-    if (cin > 256 || cout > 256 || cin < 8 || cout < 8) return APRNET_ERR_UNSUPPORTED;
+    if (cin > 256 || cout > 256) return APRNET_ERR_UNSUPPORTED;      // (narrow layers included: the padding costs no memory traffic)
     cudaStream_t st = (cudaStream_t) stream;
     const ll elems = (ll) cin * cout;
     int dev = 0, sms = 148;

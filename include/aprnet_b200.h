@@ -240,7 +240,8 @@ int aprnet_conv111_backward_input_tc(const aprnet_apr* apr, int level_delta, int
                                      const float* grad_output, int64_t ld_out, const float* weights, float* grad_input, int64_t ld_in,
                                      void* stream);
 /* Weight gradient of the 1x1x1 convolution with bf16 operands on the tensor cores (accumulated into grad_weights, float32
- * (num_stencils, Cout, Cin)); partial: aprnet_conv111_partial_elems() floats, partial_elems its size.  Same fallback rule. */
+ * (num_stencils, Cout, Cin)); partial: aprnet_conv111_partial_elems() floats, partial_elems its size.
+ * APRNET_ERR_UNSUPPORTED above 256 channels (call aprnet_conv111_backward_weights then). */
 int aprnet_conv111_backward_weights_tc(const aprnet_apr* apr, int level_delta, int cin, int cout, int num_stencils,
                                        const float* input, int64_t ld_in, const float* grad_output, int64_t ld_out,
                                        float* grad_weights, float* partial, int64_t partial_elems, void* stream);

@@ -140,8 +140,8 @@ def test_conv111_tensor_core_path(name, cin, cout, nst, oracle, bf16_mode):
             tol = 2e-5 if (exact_inputs or min(cin, cout) < 8) else 2e-2
             assert H.rel_err(H.t2n(out[0]), want) <= tol, (name, dl, exact_inputs)
             assert H.rel_err(H.t2n(gi[0]), gi_ref) <= tol, (name, dl, exact_inputs)
-            assert H.rel_err(H.t2n(gw), gw_ref) <= tol, (name, dl, exact_inputs)
-            assert ("conv111_tc_dw" in names) == (min(cin, cout) >= 8), names
+            assert H.rel_err(H.t2n(gw), gw_ref) <= (2e-5 if exact_inputs else 2e-2), (name, dl, exact_inputs)
+            assert "conv111_tc_dw" in names, names            # the weight gradient takes the tensor cores at every width
             # an explicit per-call precision overrides the process-wide setting
             out32 = C.conv111_forward(APRPtrVector([apr]), xt, wt, ld, "fp32")
             assert H.rel_err(H.t2n(out32[0]), want) <= 1e-5
