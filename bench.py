@@ -173,7 +173,8 @@ def kernel_table(prof, steps, nparts, ntree, peaks, layers, bf16, fma_tflops=Non
     """One row per profiled kernel name: launches, time per step, algorithmic work per step and the fraction of the
     roofline that bounds it.  3x3x3 kernels carry their shape in the name; the streaming kernels are summed over the
     layers that call them.  Per operator call: flops = 54 * cin * cout * N(dl); bytes = (e * cin + 4 * cout + 2) * N
-    + e * cin * T for the 3x3x3 passes (e = 2 on the bf16 path, 4 on fp32); 4 * (cin + cout) * N for a 1x1x1 pass;
+    + e * cin * T for the 3x3x3 passes (e = 2 on the bf16 path, 4 on fp32); 4 * (cin + cout) * N for a 1x1x1 pass (forward,
+    input gradient or weight gradient);
     4 * c * (N + 2 T) + 36 T for a tree fill (children read, node written and read by its parent, child table) and
     4 * c * (2 N + 2 T) + 36 T for its adjoint; 6 * c * rows for a packing pass; 4 / 8 / 8 / 12 bytes per element for
     the four GroupNorm passes.  Pooling / up-sampling (part kernel, part strided copy) and the per-(target, tap) sums of the
@@ -188,9 +189,21 @@ def kernel_table(prof, steps, nparts, ntree, peaks, layers, bf16, fma_tflops=Non
         "tree_mean_fwd": sum(4.0 * ci * (nparts[dl] + 2 * ntree[dl]) + 36.0 * ntree[dl] for ci, co, dl in c333),
         "tree_mean_bwd": sum(4.0 * ci * (2 * nparts[dl] + 2 * ntree[dl]) + 36.0 * ntree[dl] for ci, co, dl in c333 if (ci, co, dl) != first),
         "pack_rows_bf16": sum(6.0 * ci * (nparts[dl] + ntree[dl]) for ci, co, dl in c333 if ci > 4) + sum(6.0 * co * nparts[dl] for ci, co, dl in c333 if (ci, co, dl) != first),
-        "conv111": sum(2 * 4.0 * (ci + co) * nparts[dl] for ci, co, dl in c111),
-        "conv111_dw": sum(4.0 * (ci + co) * nparts[dl] for ci, co, dl in c111),
     }
+    # 1x1x1 passes: the tensor-core forward / input-gradient kernel carries its shape in the name (conv111_tc:ci..:co..:dl..,
+    # channel roles swapped in the input gradient); the CUDA-core kernel "conv111" ran the layers no such name covers.
+    # The weight gradient runs under one name in either arithmetic.
+    tc111 = set()
+    for name in prof:
+        parts = name.split(":")
+        if parts[0] == "conv111_tc" and len(parts) == 4:
+            a, b, d = int(parts[1][2:]), int(parts[2][2:]), int(parts[3][2:])
+            tc111.update([(a, b, d), (b, a, d)])
+    agg["conv111"] = sum(2 * 4.0 * (ci + co) * nparts[dl] for ci, co, dl in c111 if (ci, co, dl) not in tc111)
+    dw111 = sum(4.0 * (ci + co) * nparts[dl] for ci, co, dl in c111)
+    if "conv111_tc_dw" in prof and "conv111_dw" in prof:
+        dw111 = None                                                   # mixed: no per-name split
+    agg["conv111_dw"] = agg["conv111_tc_dw"] = dw111
     for name, bpe in GN_BYTES.items():
         agg[name] = sum(bpe * c * nparts[dl] for c, dl in gn)
     rows = []
@@ -207,6 +220,8 @@ def kernel_table(prof, steps, nparts, ntree, peaks, layers, bf16, fma_tflops=Non
                 e = 4.0 if fam.startswith("conv333_small") else e_in
                 flops = n_ops * 54.0 * ci * co * nparts[dl]
                 byts = n_ops * ((e * ci + 4.0 * co + 2.0) * nparts[dl] + e * ci * ntree[dl])
+            elif fam == "conv111_tc":
+                byts = 4.0 * (ci + co) * nparts[dl] * (calls / steps)
         elif name in agg:
             byts = agg[name]
         if byts:
