@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(TPB) conv333_backward_input_kernel(SegTable se
         for (int tap = 0; tap < 27; ++tap) {
             // gather from the same-level location at the mirrored offset
             const int32_t j = nbr[(ll) (26 - tap) * N + q];
-            if (!cross_only && j >= lo && j < hi) {
+            if (cross_only != 1 && j >= lo && j < hi) {
                 const T* g = gout + (ll) o0 * ld_out + j;
                 const T* wt = wsm + tap * OB * IB;
                 for (int o = 0; o < ob; ++o) {
@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(TPB) conv333_backward_input_kernel(SegTable se
             // scatter to a cross-level source
             const int32_t t = nbr[(ll) tap * N + q];
             const bool coarser = t >= 0 && t < lo;
-            if (coarser || t < APRNET_NONE) {
+            if (cross_only != 2 && (coarser || t < APRNET_NONE)) {
                 T s[IB];
 #pragma unroll
                 for (int i = 0; i < IB; ++i) s[i] = 0;
@@ -180,11 +180,63 @@ __global__ void __launch_bounds__(TPB) conv333_backward_input_kernel(SegTable se
             }
         }
     }
-    if (active && !cross_only) {
+    if (active && cross_only != 1) {
 #pragma unroll
         for (int i = 0; i < IB; ++i)
             if (i0 + i < cin) atomicAdd(gin + (ll) (i0 + i) * ld_in + q, acc[i]);
     }
+}
+
+// Cross-level part of the input gradient as a PULL over the cached edge plan (deterministic: one thread owns a target and
+// IB input channels and visits taps, then the locations of each (target, tap) group, in ascending order):
+//   grad[target][i] += sum over taps, locations q of the group, output channels o of dO[o][q] * w[slot][o][i][tap].
+// Replaces the atomicAdd scatter of conv333_backward_input_kernel (cross_only = 2 there leaves the scatter out).
+template<typename T, int OB, int IB, int TPB>
+__global__ void __launch_bounds__(TPB) conv333_cross_pull_kernel(const int32_t* __restrict__ active, const int32_t* __restrict__ vnbr, ll n_active,
+                                                                 ll a_begin, ll a_end, const int32_t* __restrict__ vstart,
+                                                                 const int32_t* __restrict__ vsrc, const T* __restrict__ gout, ll ld_out,
+                                                                 const T* __restrict__ wslot, T* __restrict__ gin, ll ld_in,
+                                                                 T* __restrict__ gtree, ll ld_tree, ll n_split, int cin, int cout) {
+    extern __shared__ unsigned char smem_raw[];
+    T* wsm = reinterpret_cast<T*>(smem_raw);                      // [27][OB][IB]
+    const ll a = a_begin + (ll) blockIdx.x * TPB + threadIdx.x;
+    const bool live = a < a_end;
+    const int i0 = blockIdx.y * IB;
+    T acc[IB];
+#pragma unroll
+    for (int i = 0; i < IB; ++i) acc[i] = 0;
+    for (int o0 = 0; o0 < cout; o0 += OB) {
+        __syncthreads();
+        for (int e = threadIdx.x; e < 27 * IB * OB; e += TPB) {
+            const int tap = e % 27, i = (e / 27) % IB, o = e / (27 * IB);
+            const bool ok = (o0 + o < cout) && (i0 + i < cin);
+            wsm[(tap * OB + o) * IB + i] = ok ? wslot[((ll) (o0 + o) * cin + (i0 + i)) * 27 + tap] : T(0);
+        }
+        __syncthreads();
+        if (!live) continue;
+        const int ob = min(OB, cout - o0);
+        for (int tap = 0; tap < 27; ++tap) {
+            const int32_t v = vnbr[(ll) tap * n_active + a];
+            if (v < 0) continue;
+            const T* wt = wsm + tap * OB * IB;
+            const int e1 = vstart[v + 1];
+            for (int e = vstart[v]; e < e1; ++e) {
+                const T* g = gout + (ll) o0 * ld_out + vsrc[e];
+                for (int o = 0; o < ob; ++o) {
+                    const T d = g[(ll) o * ld_out];
+#pragma unroll
+                    for (int i = 0; i < IB; ++i) acc[i] = fma(d, wt[o * IB + i], acc[i]);
+                }
+            }
+        }
+    }
+    if (!live) return;
+    const ll t = active[a];
+    T* dst = t < n_split ? gin + (ll) i0 * ld_in + t : gtree + (ll) i0 * ld_tree + (t - n_split);
+    const ll ldd = t < n_split ? ld_in : ld_tree;
+#pragma unroll
+    for (int i = 0; i < IB; ++i)
+        if (i0 + i < cin) dst[(ll) i * ldd] += acc[i];           // the only writer of this entry in this launch
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -362,11 +414,34 @@ int conv333_bwd_input(aprnet_apr* a, int dl, int cin, int cout, int slots, const
     const SegTable segs = make_seg_table(aprnet_segments(a, dl, slots, false), TPB);
     char pname[64];
     snprintf(pname, sizeof(pname), "%s:ci%d:co%d:dl%d", cross_only ? "conv333_bwd_cross" : "conv333_bwd_input", cin, cout, dl);
+    // complete pass: the cross-level part is pulled over the edge plan (fixed summation order) where the plan's 32-bit edge
+    // ids suffice; the atomic scatter remains for larger structures and for the cross-only entry point
+    EdgePlan* ep = (!cross_only && 27 * plan->n + 1 < (1ll << 31)) ? aprnet_get_edge_plan(a, dl, st) : nullptr;
+    if (!cross_only && 27 * plan->n + 1 < (1ll << 31) && !ep) return APRNET_ERR_CUDA;
+    const int mode = ep ? 2 : cross_only;
     if (segs.tile_begin[segs.n] > 0) {
         int rc;
-        if (cin <= 4) rc = launch_backward_input<T, 8, 4, TPB>(segs, plan, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout, st, pname, cross_only);
-        else rc = launch_backward_input<T, 8, 16, TPB>(segs, plan, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout, st, pname, cross_only);
+        if (cin <= 4) rc = launch_backward_input<T, 8, 4, TPB>(segs, plan, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout, st, pname, mode);
+        else rc = launch_backward_input<T, 8, 16, TPB>(segs, plan, gout, ld_out, w, gin, ld_in, gtree, ld_tree, cin, cout, st, pname, mode);
         if (rc) return rc;
+    }
+    if (ep && ep->n_active > 0) {
+        constexpr int OB = 8, IB = 16;
+        const size_t smem = (size_t) 27 * IB * OB * sizeof(T);
+        auto kern = conv333_cross_pull_kernel<T, OB, IB, TPB>;
+        if (smem > 48 * 1024) APRNET_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        const int cml = a->cml(dl);
+        char pname2[64];
+        snprintf(pname2, sizeof(pname2), "conv333_bwd_cross_pull:ci%d:co%d:dl%d", cin, cout, dl);
+        for (const ActiveSeg& sg : ep->segs) {
+            if (sg.end <= sg.begin) continue;
+            const int slot = std::min(cml - sg.location_level, slots - 1);
+            dim3 grid((unsigned) aprnet_ceil_div(sg.end - sg.begin, TPB), (unsigned) aprnet_ceil_div(cin, IB));
+            AprnetProfScope _prof(pname2, st);
+            kern<<<grid, TPB, smem, st>>>(ep->active, ep->vnbr, ep->n_active, sg.begin, sg.end, ep->vstart, ep->vsrc, gout, ld_out,
+                                          w + (ll) slot * cout * cin * 27, gin, ld_in, gtree, ld_tree, plan->n, cin, cout);
+        }
+        APRNET_LAUNCH_CHECK();
     }
     if (!tree_adjoint) return APRNET_OK;
     return aprnet_fill_tree_mean_backward(a, dl, sizeof(T) == 4 ? APRNET_F32 : APRNET_F64, cin, gin, ld_in, gtree, ld_tree, st);

@@ -158,3 +158,33 @@ def test_maxpool_upsample(name, dtype, oracle, dev):
             gu = rng.randn(5, o.number_parts(dl - 1)).astype(NP[dtype])
             gin = C.upsample_const_backward(APRPtrVector([apr]), torch.from_numpy(gu).to(dev)[None].contiguous(), ld)
             assert H.rel_err(H.t2n(gin[0]), o.upsample_backward(gu.astype(np.float64), dl)) <= TOL[dtype]
+
+
+def test_conv333_fp32_input_gradient_is_deterministic(oracle, dev):
+    """The CUDA-core path pulls the cross-level part of the input gradient over the cached edge plan (no atomic adds
+    between locations): two calls give bit-identical results, and they agree with the oracle."""
+    from _pyaprwrapper.aprnet import cuda as C
+    from _pyaprwrapper.data_containers import APRPtrVector
+    a, apr, o = make("blob", oracle)
+    rng = np.random.RandomState(21)
+    cin, cout = 19, 24
+    L = a.level_max - a.level_min + 1
+    for dl in range(0, H.max_dl(a) + 1):
+        n = o.number_parts(dl)
+        x = rng.rand(cin, n).astype(np.float32)
+        w = (rng.randn(L, cout, cin, 3, 3, 3) / np.sqrt(27 * cin)).astype(np.float32)
+        go = rng.randn(cout, n).astype(np.float32)
+        ld = torch.full((1,), dl, dtype=torch.int32)
+        xt = torch.from_numpy(x).to(dev)[None].contiguous()
+        wt = torch.from_numpy(w).to(dev)
+        got = torch.from_numpy(go).to(dev)[None].contiguous()
+        C.profile_read(); C.profile_enable(True)
+        gi1, gw1 = C.conv333_backward(APRPtrVector([apr]), xt, wt, got, ld)
+        gi2, gw2 = C.conv333_backward(APRPtrVector([apr]), xt, wt, got, ld)
+        torch.cuda.synchronize()
+        C.profile_enable(False)
+        names = set(k.split(":")[0] for k in C.profile_read())
+        assert "conv333_bwd_cross_pull" in names or dl > 0, (dl, names)      # (coarse level deltas of this small APR may have one level only)
+        assert torch.equal(gi1, gi2) and torch.equal(gw1, gw2), dl
+        gi_ref, _ = o.conv333_backward(x.astype(np.float64), w.astype(np.float64), go.astype(np.float64), dl)
+        assert H.rel_err(H.t2n(gi1[0]), gi_ref) <= 1e-5, dl
