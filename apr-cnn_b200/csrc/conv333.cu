@@ -7,8 +7,9 @@
 // resolution is a cached neighbour table (27 int32 per output location, apr_handle.cu), and
 //   * forward: one thread owns one output location and a block of output channels, loops over all
 //     input channels and taps, and writes each output exactly once;
-//   * input gradient: same-level taps are gathered through the mirrored table entry (no atomics);
-//     only cross-level taps (parent-level particle, tree node) are scattered with atomicAdd;
+//   * input gradient: same-level taps are gathered through the mirrored table entry; cross-level taps (parent-level
+//     particle, tree node) are pulled per target over the cached edge plan in a fixed order (conv333_cross_pull_kernel;
+//     an atomicAdd scatter remains for structures too large for the plan's 32-bit edge ids);
 //   * weight gradient: block-local partial sums in registers over a contiguous particle range,
 //     written to a workspace and reduced in a fixed order (deterministic).
 // Arithmetic: pyapr/aprnet/src/conv.hpp:83-195,289-481 and helpers.hpp:358-478,505-704.
@@ -116,7 +117,8 @@ __global__ void __launch_bounds__(TPB) conv333_forward_kernel(SegTable segs, con
 // Thread = output location q, block of IB input channels (grid.y); output channels staged OB at a
 // time.  For tap t (offset d): if the cell at -d holds a same-level output location j (mirrored table
 // entry 26 - t) then q receives W[t]^T dO[j]: a gather.  If the cell at +d resolved to a coarser
-// particle or a tree node, W[t]^T dO[q] is scattered there with atomicAdd.
+// particle or a tree node, W[t]^T dO[q] is scattered there with atomicAdd (cross_only = 0 or 1; with cross_only = 2 the
+// scatter is left to conv333_cross_pull_kernel).
 template<typename T, int OB, int IB, int TPB>
 __global__ void __launch_bounds__(TPB) conv333_backward_input_kernel(SegTable segs, const int32_t* __restrict__ nbr, ll N,
                                                                      const T* __restrict__ gout, ll ld_out,
