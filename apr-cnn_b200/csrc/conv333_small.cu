@@ -69,20 +69,25 @@ __global__ void __launch_bounds__(128) conv333_small_forward_kernel(SegTable seg
     float acc[32];
 #pragma unroll
     for (int o = 0; o < 32; ++o) acc[o] = 0.f;
-    ll rows[27];
+    // all 27 table entries, then all 27 values of a channel, are requested before any is used (the kernel is bound by
+    // the latency of these gathers, not by a unit); row numbers fit 32 bits (N + T + 1 < 2^31, checked by the driver)
+    int32_t rows[27];
 #pragma unroll
-    for (int tap = 0; tap < 27; ++tap) rows[tap] = resolve_row(__ldg(nbr + (ll) tap * N + p), N, N + T);
+    for (int tap = 0; tap < 27; ++tap) rows[tap] = (int32_t) resolve_row(__ldg(nbr + (ll) tap * N + p), N, N + T);
+#pragma unroll 1
+    for (int ci = 0; ci < CIN; ++ci) {
+        float v[27];
+        const float* vc = vals + (ll) ci * R;
 #pragma unroll
-    for (int tap = 0; tap < 27; ++tap) {
+        for (int tap = 0; tap < 27; ++tap) v[tap] = __ldg(vc + rows[tap]);
 #pragma unroll
-        for (int ci = 0; ci < CIN; ++ci) {
-            const float v = __ldg(vals + (ll) ci * R + rows[tap]);
+        for (int tap = 0; tap < 27; ++tap) {
             const F4* wr = ws + (tap * CIN + ci) * 8;
 #pragma unroll
             for (int o4 = 0; o4 < 8; ++o4) {
                 const F4 q = wr[o4];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) acc[4 * o4 + k] = fmaf(v, q.a[k], acc[4 * o4 + k]);
+                for (int k = 0; k < 4; ++k) acc[4 * o4 + k] = fmaf(v[tap], q.a[k], acc[4 * o4 + k]);
             }
         }
     }
