@@ -46,7 +46,15 @@ __global__ void __launch_bounds__(GN_TPB) gn_partial_stats_kernel(const T* __res
     const ll b0 = (ll) blockIdx.x * chunk_len, b1 = min(n, b0 + chunk_len);
     const T* xr = x + row * n;
     double s = 0.0, ss = 0.0;
-    for (ll i = b0 + threadIdx.x; i < b1; i += GN_TPB) { const double v = (double) xr[i]; s += v; ss += v * v; }
+    ll i = b0 + threadIdx.x;
+    for (; i + 3 * GN_TPB < b1; i += 4 * GN_TPB) {        // four independent loads in flight; same summation order
+        T v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = xr[i + u * GN_TPB];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { const double d = (double) v[u]; s += d; ss += d * d; }
+    }
+    for (; i < b1; i += GN_TPB) { const double v = (double) xr[i]; s += v; ss += v * v; }
     block_sum2(s, ss);
     if (threadIdx.x == 0) { partial[(row * nchunks + blockIdx.x) * 2] = s; partial[(row * nchunks + blockIdx.x) * 2 + 1] = ss; }
 }
@@ -103,12 +111,20 @@ __global__ void __launch_bounds__(GN_TPB) gn_backward_partial_kernel(const T* __
     const T* xr = x + row * n;
     const T* dr = dy + row * n;
     double s = 0.0, sx = 0.0;
-    for (ll i = b0 + threadIdx.x; i < b1; i += GN_TPB) {
-        const T xh = (xr[i] - mu) * rs;
-        T d = dr[i];
+    auto add = [&](T xv, T d) {
+        const T xh = (xv - mu) * rs;
         if (relu && xh * ga + be <= T(0)) d = T(0);
         s += (double) d; sx += (double) d * (double) xh;
+    };
+    ll i = b0 + threadIdx.x;
+    for (; i + 3 * GN_TPB < b1; i += 4 * GN_TPB) {        // eight independent loads in flight; same summation order
+        T xv[4], dv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { xv[u] = xr[i + u * GN_TPB]; dv[u] = dr[i + u * GN_TPB]; }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) add(xv[u], dv[u]);
     }
+    for (; i < b1; i += GN_TPB) add(xr[i], dr[i]);
     block_sum2(s, sx);
     if (threadIdx.x == 0) { partial[(row * nchunks + blockIdx.x) * 2] = s; partial[(row * nchunks + blockIdx.x) * 2 + 1] = sx; }
 }
