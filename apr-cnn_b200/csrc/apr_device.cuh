@@ -69,7 +69,11 @@ struct aprnet_apr {
     float* tree_scale = nullptr;         // [n_tree] weight of each child in its parent's mean
     std::map<int, AprPlan> plans;
     std::map<int, EdgePlan> edge_plans;
-    long long device_bytes = 0;
+    // parent tree node of every tree node (-1: none) and, per level delta, of every feature location (particle or
+    // upgraded node); built on first use by the tree-mean adjoint (aprnet_node_parent_table / aprnet_loc_parent_table)
+    mutable int32_t* node_parent = nullptr;
+    mutable std::map<int, int32_t*> loc_parent;
+    mutable long long device_bytes = 0;
 
     int cml(int dl) const { return meta.level_max - dl; }
     long long number_parts(int dl) const {
@@ -113,6 +117,8 @@ struct Segment { long long begin, end; int slot; int level; };
 std::vector<Segment> aprnet_segments(const aprnet_apr* apr, int dl, int num_slots, bool merge);
 
 const AprPlan* aprnet_get_plan(aprnet_apr* apr, int dl, cudaStream_t stream);
+const int32_t* aprnet_node_parent_table(const aprnet_apr* apr, cudaStream_t stream);            // nullptr on failure
+const int32_t* aprnet_loc_parent_table(const aprnet_apr* apr, int dl, cudaStream_t stream);     // nullptr on failure
 
 // Optional per-kernel timing (aprnet_profile_enable): brackets a launch site with two CUDA events on
 // the launching stream.  Costs nothing when profiling is off.

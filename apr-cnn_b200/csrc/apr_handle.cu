@@ -296,6 +296,8 @@ extern "C" void aprnet_apr_destroy(aprnet_apr* a) {
     cudaFree(a->row_ptr); cudaFree(a->y); cudaFree(a->tree_row_ptr); cudaFree(a->tree_y);
     cudaFree(a->child); cudaFree(a->tree_scale);
     for (auto& kv : a->plans) cudaFree(kv.second.nbr);
+    cudaFree(a->node_parent);
+    for (auto& kv : a->loc_parent) cudaFree(kv.second);
     for (auto& kv : a->edge_plans) aprnet_free_edge_plan(kv.second);
     delete a;
     if (prev >= 0) cudaSetDevice(prev);
@@ -354,9 +356,74 @@ const AprPlan* aprnet_get_plan(aprnet_apr* a, int dl, cudaStream_t stream) {
     return &res.first->second;
 }
 
+// Parent tables from the child table: every child slot of tree node t names a particle (v >= 0), a tree node (coded) or,
+// at the finest tree level of a level delta > 0 (use_up), an upgraded node that lives in the feature vector at
+// up_off + index.  Either output may be null.
+__global__ void build_parent_tables_kernel(const int32_t* __restrict__ child, long long n_tree, long long tb, long long te,
+                                           long long up_off, int use_up, int32_t* __restrict__ loc_parent, int32_t* __restrict__ node_parent) {
+    const long long t = tb + (long long) blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= te) return;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        const int32_t v = child[(long long) s * n_tree + t];
+        if (v >= 0) { if (loc_parent) loc_parent[v] = (int32_t) t; }
+        else if (v != APRNET_NONE) {
+            if (use_up) { if (loc_parent) loc_parent[aprnet_dec_tree(v) + up_off] = (int32_t) t; }
+            else if (node_parent) node_parent[aprnet_dec_tree(v)] = (int32_t) t;
+        }
+    }
+}
+
+static int32_t* alloc_minus_one(const aprnet_apr* a, long long n, cudaStream_t stream, const char* what) {
+    int32_t* p = nullptr;
+    n = std::max<long long>(n, 1);
+    if (cudaMalloc((void**) &p, (size_t) n * sizeof(int32_t)) != cudaSuccess) {
+        aprnet_set_error("%s: cudaMalloc of %zu bytes failed", what, (size_t) n * sizeof(int32_t));
+        cudaGetLastError();
+        return nullptr;
+    }
+    a->device_bytes += n * (long long) sizeof(int32_t);
+    cudaMemsetAsync(p, 0xFF, (size_t) n * sizeof(int32_t), stream);
+    return p;
+}
+
+const int32_t* aprnet_node_parent_table(const aprnet_apr* a, cudaStream_t stream) {
+    if (a->node_parent) return a->node_parent;
+    int32_t* tab = alloc_minus_one(a, a->n_tree, stream, "aprnet_node_parent_table");
+    if (!tab) return nullptr;
+    const LevelMeta& m = a->meta;
+    for (int lp = m.level_min - 1; lp <= m.level_max - 1; ++lp) {
+        const long long tb = m.tlvl_begin[lp], te = m.tlvl_begin[lp + 1];
+        if (te > tb) build_parent_tables_kernel<<<aprnet_ceil_div(te - tb, 256), 256, 0, stream>>>(a->child, a->n_tree, tb, te, 0, 0, nullptr, tab);
+    }
+    if (cudaGetLastError() != cudaSuccess) { aprnet_set_error("aprnet_node_parent_table: kernel launch failed"); cudaFree(tab); return nullptr; }
+    a->node_parent = tab;
+    return tab;
+}
+
+const int32_t* aprnet_loc_parent_table(const aprnet_apr* a, int dl, cudaStream_t stream) {
+    auto it = a->loc_parent.find(dl);
+    if (it != a->loc_parent.end()) return it->second;
+    int32_t* tab = alloc_minus_one(a, a->number_parts(dl), stream, "aprnet_loc_parent_table");
+    if (!tab) return nullptr;
+    const LevelMeta& m = a->meta;
+    const int cml = a->cml(dl);
+    const long long up = (dl > 0) ? a->tree_offset(cml) : 0;
+    for (int lp = m.level_min - 1; lp <= cml - 1; ++lp) {
+        const long long tb = m.tlvl_begin[lp], te = m.tlvl_begin[lp + 1];
+        if (te > tb) build_parent_tables_kernel<<<aprnet_ceil_div(te - tb, 256), 256, 0, stream>>>(a->child, a->n_tree, tb, te, up,
+                                                                                                 (dl > 0 && lp + 1 == cml) ? 1 : 0, tab, nullptr);
+    }
+    if (cudaGetLastError() != cudaSuccess) { aprnet_set_error("aprnet_loc_parent_table: kernel launch failed"); cudaFree(tab); return nullptr; }
+    a->loc_parent.emplace(dl, tab);
+    return tab;
+}
+
 extern "C" int aprnet_plan_build(aprnet_apr* a, int dl, void* stream) {
     APRNET_ARG_CHECK(a && a->valid_dl(dl), "bad handle or level_delta");
-    return aprnet_get_plan(a, dl, (cudaStream_t) stream) ? APRNET_OK : APRNET_ERR_CUDA;
+    if (!aprnet_get_plan(a, dl, (cudaStream_t) stream)) return APRNET_ERR_CUDA;
+    if (!aprnet_node_parent_table(a, (cudaStream_t) stream) || !aprnet_loc_parent_table(a, dl, (cudaStream_t) stream)) return APRNET_ERR_CUDA;
+    return APRNET_OK;
 }
 
 extern "C" int aprnet_plan_copy_nbr_table(aprnet_apr* a, int dl, int32_t* host_out) {

@@ -63,45 +63,30 @@ __global__ void __launch_bounds__(TPB) tree_mean_level_kernel(const int32_t* __r
     }
 }
 
-// adjoint of one level: every child of t receives scale[t] * grad_tree[t]
+// Adjoint, child-centric: entry u of `dst` (a tree node of one level, or a feature location) receives
+// scale[t] * grad_tree[t] of its parent node t = parent[u].  One thread per child and CH_PER_BLOCK channels: the child
+// axis is streamed (coalesced read-modify-write, one writer per entry), the parents' values come from a few cache lines
+// per warp.  The parent-centric form (one thread per parent, eight scattered children) touched every sector of the
+// gradient half at a time and ran at half this speed.  dst and gtree may be the same array (node levels): a level only
+// reads the level above it.
 template<typename T>
-__global__ void tree_mean_level_backward_kernel(const int32_t* __restrict__ child, const float* __restrict__ scale,
-                                                ll n_tree, ll tb, ll te, T* __restrict__ gin, ll ld_in,
-                                                T* __restrict__ gtree, ll ld_tree, int C, ll up_off, int use_up) {
-    const ll t = tb + (ll) blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= te) return;
-    ll off[8];
-    bool to_tree[8], present[8];
-#pragma unroll
-    for (int s = 0; s < 8; ++s) {
-        const int32_t v = child[(ll) s * n_tree + t];
-        present[s] = v != APRNET_NONE;
-        to_tree[s] = v < APRNET_NONE && !use_up;
-        off[s] = v >= 0 ? (ll) v : (v == APRNET_NONE ? 0 : aprnet_dec_tree(v) + (use_up ? up_off : 0));
-    }
-    const T f = (T) scale[t];
+__global__ void __launch_bounds__(TPB) tree_mean_backward_children_kernel(const int32_t* __restrict__ parent, const float* __restrict__ scale,
+                                                                          ll ub, ll ue, T* dst, ll ld_dst, const T* gtree, ll ld_tree, int C) {
+    const ll u = ub + (ll) blockIdx.x * blockDim.x + threadIdx.x;
+    if (u >= ue) return;
     const int c0 = blockIdx.y * CH_PER_BLOCK;
+    T old[CH_PER_BLOCK];
+#pragma unroll
+    for (int k = 0; k < CH_PER_BLOCK; ++k) old[k] = dst[(ll) min(c0 + k, C - 1) * ld_dst + u];        // independent of the parent
+    const int32_t t = parent[u];
+    if (t < 0) return;
+    const T f = (T) scale[t];
     T g[CH_PER_BLOCK];
 #pragma unroll
-    for (int k = 0; k < CH_PER_BLOCK; ++k) g[k] = f * gtree[(ll) min(c0 + k, C - 1) * ld_tree + t];
-    T old[CH_PER_BLOCK][8];
+    for (int k = 0; k < CH_PER_BLOCK; ++k) g[k] = gtree[(ll) min(c0 + k, C - 1) * ld_tree + t];
 #pragma unroll
-    for (int k = 0; k < CH_PER_BLOCK; ++k) {
-        const int c = min(c0 + k, C - 1);
-#pragma unroll
-        for (int s = 0; s < 8; ++s) old[k][s] = present[s] ? (to_tree[s] ? gtree[(ll) c * ld_tree + off[s]] : gin[(ll) c * ld_in + off[s]]) : T(0);
-    }
-#pragma unroll
-    for (int k = 0; k < CH_PER_BLOCK; ++k) {
-        if (c0 + k >= C) break;
-        const int c = c0 + k;
-#pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            if (!present[s]) continue;
-            if (to_tree[s]) gtree[(ll) c * ld_tree + off[s]] = old[k][s] + g[k];
-            else gin[(ll) c * ld_in + off[s]] = old[k][s] + g[k];
-        }
-    }
+    for (int k = 0; k < CH_PER_BLOCK; ++k)
+        if (c0 + k < C) dst[(ll) (c0 + k) * ld_dst + u] = old[k] + f * g[k];
 }
 
 template<typename T>
@@ -238,14 +223,21 @@ template<typename T>
 int fill_tree_mean_bwd(const aprnet_apr* a, int dl, int C, T* gin, ll ld_in, T* gtree, ll ld_tree, cudaStream_t st) {
     const LevelMeta& m = a->meta;
     const int cml = a->cml(dl);
-    const ll up = (dl > 0) ? a->tree_offset(cml) : 0;
-    for (int lp = m.level_min - 1; lp <= cml - 1; ++lp) {
-        const ll tb = m.tlvl_begin[lp], te = m.tlvl_begin[lp + 1];
-        if (te <= tb) continue;
-        { AprnetProfScope _prof("tree_mean_bwd", st);
-        tree_mean_level_backward_kernel<T><<<node_grid(te - tb, C), TPB, 0, st>>>(
-            a->child, a->tree_scale, a->n_tree, tb, te, gin, ld_in, gtree, ld_tree, C, up, (dl > 0 && lp + 1 == cml) ? 1 : 0);
-        }
+    const int32_t* node_parent = aprnet_node_parent_table(a, st);
+    const int32_t* loc_parent = aprnet_loc_parent_table(a, dl, st);
+    if (!node_parent || !loc_parent) return APRNET_ERR_CUDA;
+    // tree nodes, coarse to fine: level l receives from level l - 1, whose gradient is complete by then
+    for (int l = m.level_min; l <= cml - 1; ++l) {
+        const ll ub = m.tlvl_begin[l], ue = m.tlvl_begin[l + 1];
+        if (ue <= ub) continue;
+        AprnetProfScope _prof("tree_mean_bwd", st);
+        tree_mean_backward_children_kernel<T><<<node_grid(ue - ub, C), TPB, 0, st>>>(node_parent, a->tree_scale, ub, ue, gtree, ld_tree, gtree, ld_tree, C);
+    }
+    // then every feature location (particles of all levels, upgraded nodes) from its parent node
+    const ll n = a->number_parts(dl);
+    if (n > 0) {
+        AprnetProfScope _prof("tree_mean_bwd", st);
+        tree_mean_backward_children_kernel<T><<<node_grid(n, C), TPB, 0, st>>>(loc_parent, a->tree_scale, 0, n, gin, ld_in, gtree, ld_tree, C);
     }
     APRNET_LAUNCH_CHECK();
     return APRNET_OK;
