@@ -3,7 +3,8 @@
 // All four are child <-> parent transfers along the APR tree.  They run as index-driven gathers over
 // the cached child table: one thread per parent tree node, eight child slots, channels looped inside
 // the thread so the indices are read once.  Consecutive threads hold consecutive nodes of a sparse
-// row, whose children are consecutive in the child rows, so the value accesses coalesce.
+// row, whose children are consecutive in the child rows, so the value accesses coalesce.  The adjoint of the
+// tree mean is the exception: it runs child-centric over cached parent tables (see its kernel).
 // Arithmetic follows pyapr/aprnet/src/helpers.hpp:156-350 (tree mean and its adjoint),
 // pyapr/aprnet/src/maxpool.hpp:70-230 and pyapr/aprnet/src/upsample.hpp:70-236.
 #include "apr_device.cuh"
